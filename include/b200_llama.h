@@ -29,6 +29,7 @@ extern "C" {
 
 #define B200_F32 0
 #define B200_F16 1
+#define B200_BF16 2 /* bfloat16 storage, fp32 accumulation: the ops of b200_serve.h (layer norm, grouped GEMM, latent attention, MoE) */
 
 #define B200_OK 0
 #define B200_EINVAL (-1)       /* bad shape / null pointer / misalignment */

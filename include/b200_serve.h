@@ -1,0 +1,158 @@
+/*
+ * b200_serve.h — C ABI of the model-family layer of the library: a registry that picks the model class from a
+ * checkpoint folder's config.json, a step function over a batch of (sequence slot, next tokens) entries with a paged
+ * cache behind it, a continuous-batching scheduler with greedy sampling on top, and the kernels that the families
+ * beyond LLaMA bring (layer norm pairs, grouped GEMM, latent attention with a softmax sink, mixture-of-experts
+ * routing). b200_engine.h stays the LLaMA hot path; b200_model_open wraps it for checkpoints of that family.
+ *
+ * Families: "Nekodra" (config.json + model.safetensors: parallel layers of latent attention without positions and a
+ * routed feed-forward with identity experts), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
+ * a config.json naming the b200_model_config fields).
+ */
+#ifndef B200_SERVE_H
+#define B200_SERVE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "b200_llama.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------------------
+ * kernels
+ * --------------------------------------------------------------------------------------------- */
+
+/* out[t,:] = table[ids[t],:] + pos_table[pos[t],:] as fp32 (the residual stream is fp32); tables of `dtype` */
+int b200_embed_positions(const int* ids, const int* pos, const void* table, const void* pos_table, float* out,
+                         int n_tokens, int width, int dtype, void* stream);
+
+/* Layer norm with weight and bias, up to two (w, b) pairs applied to the SAME rows of x (mean and variance are
+ * computed once, two-pass, in fp32): out_k[i,:] = (x[r_i,:] - mean) / sqrt(var + eps) * w_k + b_k, r_i = rows ? rows[i]
+ * : i. x fp32 [*, width]; w, b fp32; out1 / out2 of out_dtype (out2, w2, b2 may be NULL). */
+int b200_layernorm_pair(const float* x, const int* rows, int n_rows, int width, float eps, const float* w1,
+                        const float* b1, void* out1, const float* w2, const float* b2, void* out2, int out_dtype,
+                        void* stream);
+
+/* epilogues of b200_gemm_grouped */
+#define B200_GG_NONE 0
+#define B200_GG_SIGMOID_MUL 1 /* C = acc * sigmoid(aux[row, col])                                   */
+#define B200_GG_GLU 2         /* C = silu(A W[0:N]^T) * (A W[N:2N]^T); W has 2N rows; trans_b only  */
+
+typedef struct b200_gemm_grouped_args {
+    const void* A; const void* W; void* C;
+    const float* aux;          /* SIGMOID_MUL: fp32 [rows, ld_aux] (+ batch * stride_aux)                       */
+    const int* a_rows;         /* device: source row of A for each logical row (NULL = identity)               */
+    const int* group_off;      /* device [batch + 1]: group g owns logical rows [off[g], off[g+1]) (NULL = none) */
+    long long lda, ldw, ldc, ld_aux;                       /* leading dimensions in elements                   */
+    long long stride_a, stride_w, stride_c, stride_aux;    /* per batch (stride_w also per group), in elements */
+    int M;                     /* rows (groups: an upper bound of the rows of one group)                        */
+    int N, K;
+    int batch;                 /* batches or groups (grid z)                                                     */
+    int trans_b;               /* 1: W is [N, K] (ldw >= K); 0: W is [K, N] (ldw >= N)                           */
+    int epi;
+    int a_dtype, w_dtype, c_dtype;   /* B200_F32 / B200_BF16                                                   */
+} b200_gemm_grouped_args;
+int b200_gemm_grouped(const b200_gemm_grouped_args* args, void* stream);
+
+/* Latent cache rows: for token t, row = raw[t, 0:rank] (fp32, leading dimension ld_raw) divided by its root mean
+ * square (eps inside the root) times w, stored as `dtype` at position pos[t] of sequence slot[t]:
+ * pool[(pages[slot[t] * max_pages + pos[t] / page_rows] * page_rows + pos[t] % page_rows) * rank + :]. */
+int b200_latent_store(const float* raw, long long ld_raw, const float* w, float eps, void* pool, const int* pages,
+                      int max_pages, int page_rows, const int* slot, const int* pos, int n_tokens, int rank, int dtype,
+                      void* stream);
+
+/* Attention over cached latent rows in absorbed form, with a softmax sink. For token t (sequence slot[t], position
+ * pos[t]) and head h: s_j = scale * <qa[t,h,:], c_j> over the sequence's rows j <= pos[t]; p_j = exp(s_j - m) /
+ * (sum_j exp(s_j - m) + exp(sink[h] - m)); out[t,h,:] = sum_j p_j c_j. qa, out fp32 [n_tokens, heads, rank] (qa is the
+ * query already multiplied by the key up-projection; the caller applies the value up-projection to out). The sink
+ * has no row and no value. Rows come from the page pool as in b200_latent_store. */
+int b200_latent_attention(const float* qa, float* out, const void* pool, const int* pages, int max_pages, int page_rows,
+                          const int* slot, const int* pos, const float* sink, float scale, int n_tokens, int heads,
+                          int rank, int dtype, void* stream);
+
+/* Router of a mixture of experts with identity experts: z = h W_r^T (fp32 accumulate; h of h_dtype, W_r fp32
+ * [n_out, width]); s = softmax(z) over all n_out outputs; the `top` largest of s + correction are chosen; their weights
+ * are s * scale (no correction, not renormalised). chosen / weight: [n_tokens, top]. */
+int b200_moe_route(const void* h, int h_dtype, const float* w_router, const float* correction, int n_tokens, int width,
+                   int n_out, int top, float scale, int* chosen, float* weight, void* stream);
+/* Counting sort of the (token, choice) pairs by expert: group_off [n_experts + 1], src_row [n_tokens * top] (token of
+ * each sorted row), dest [n_tokens, top] (sorted row of each pair, -1 for chosen >= n_experts: identity experts own no
+ * rows). One launch, no host sync. */
+int b200_moe_dispatch(const int* chosen, int n_tokens, int top, int n_experts, int* group_off, int* src_row, int* dest,
+                      void* stream);
+/* x[t,:] += mix[t,:] + shared[t,:] + sum_k weight[t,k] * (dest[t,k] >= 0 ? expert_out[dest[t,k],:] : h[t,:])
+ * (fp32 sums in a fixed order; mix, shared, the routed part may each be NULL) */
+int b200_residual_combine(float* x, const float* mix, const float* shared, const float* expert_out, const int* dest,
+                          const float* weight, const void* h, int h_dtype, int n_tokens, int width, int top, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * models
+ * --------------------------------------------------------------------------------------------- */
+typedef struct b200_model b200_model;
+
+typedef struct b200_model_options {
+    int dtype;        /* B200_BF16: bfloat16 weights / operands, fp32 accumulation, residual and norms; B200_F32: all fp32 */
+    int max_tokens;   /* cache pool: live tokens, each sequence rounded up to whole pages                            */
+    int max_slots;    /* sequences alive at once                                                                    */
+    int max_step_tokens; /* most tokens one step may bring (0 = default); scratch is sized for it                   */
+} b200_model_options;
+
+const char* b200_serve_last_error(void);
+/* comma-separated names of the registered families */
+const char* b200_model_families(void);
+/* Reads dir/config.json, picks the family by its "architecture", loads the weights. NULL on failure. */
+b200_model* b200_model_open(const char* dir, const b200_model_options* opt);
+void b200_model_close(b200_model* m);
+const char* b200_model_family(const b200_model* m);
+int b200_model_vocab(const b200_model* m);
+int b200_model_width(const b200_model* m);
+int b200_model_layer_count(const b200_model* m);
+int b200_model_max_positions(const b200_model* m);
+int b200_model_page_rows(const b200_model* m);
+int b200_model_pages_total(const b200_model* m);
+int b200_model_pages_free(const b200_model* m);
+int b200_model_slot_length(const b200_model* m, int slot);   /* tokens cached for the slot */
+/* host copy of the slot's page list; returns the number of pages written (<= max_n) */
+int b200_model_slot_pages(const b200_model* m, int slot, int* out, int max_n);
+
+/* One step of the engine: entry i appends n_tokens[i] tokens (tokens packed back to back) to sequence slot slots[i]
+ * after what the slot has cached, all entries as ONE batch (prompt portions beside single decoded tokens). n_want[i]
+ * places (indices into the entry's tokens, packed in `want`) are asked for: logits_out (host, fp32 [sum n_want, vocab],
+ * may be NULL) and ids_out (host, greedy pick per wanted place, may be NULL). Pages are taken as slots grow;
+ * B200_ENOMEM when the pool is empty (nothing is run). */
+int b200_model_step(b200_model* m, int n_entries, const int* slots, const int* n_tokens, const int* tokens,
+                    const int* n_want, const int* want, float* logits_out, int* ids_out);
+/* the slot's pages go back to the pool, its length to 0 */
+int b200_model_release(b200_model* m, int slot);
+/* debugging / tests: keep the residual stream after every layer of the next steps (fp32 [layers, tokens, width]) */
+int b200_model_capture_layers(b200_model* m, int on);
+int b200_model_captured_layers(b200_model* m, float* out, size_t max_floats);
+/* kernels launched by the last step */
+int b200_model_step_launches(const b200_model* m);
+
+/* Continuous-batching generation with greedy sampling: n_requests prompts (ids packed, lens[]), at most max_slots
+ * alive at once; waiting requests are admitted when a slot and pages for their prompt + max_new tokens are free;
+ * prompts are fed in portions of at most chunk tokens per step (0 = whole) beside the other sequences' single
+ * tokens; a sequence ends at eos_id (>= 0) or after max_new tokens. out_ids [n_requests, max_new] padded with
+ * eos_id, n_generated [n_requests] (may be NULL). Returns the number of engine steps (>= 0) or an error (< 0). */
+int b200_model_generate(b200_model* m, int n_requests, const int* prompt_ids, const int* lens, int max_new, int eos_id,
+                        int chunk, int* out_ids, int* n_generated);
+
+/* ---------------------------------------------------------------------------------------------
+ * trace sessions: requests named by strings, replayed step by step (bin/trace_run)
+ * --------------------------------------------------------------------------------------------- */
+typedef struct b200_session b200_session;
+b200_session* b200_session_create(b200_model* m);
+void b200_session_destroy(b200_session* s);
+/* slot of a request id, admitting it (first free slot) when new; < 0 when no slot is free */
+int b200_session_slot(b200_session* s, const char* request_id);
+/* the request is over: its slot and pages are free again */
+int b200_session_end(b200_session* s, const char* request_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_SERVE_H */

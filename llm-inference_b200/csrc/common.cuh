@@ -2,6 +2,7 @@
 // Everything here is header-only and included by each kernel translation unit.
 #pragma once
 #include <cuda.h>
+#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -27,6 +28,12 @@ template <> struct DT<__half> {
     static constexpr int kPer16B = 8;
     static __device__ __forceinline__ float to_f(__half v) { return __half2float(v); }
     static __device__ __forceinline__ __half from_f(float v) { return __float2half_rn(v); }
+};
+
+template <> struct DT<__nv_bfloat16> {
+    static constexpr int kPer16B = 8;
+    static __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
+    static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
 // 16-byte packet: the unit every bandwidth kernel moves per thread per access.

@@ -1,0 +1,317 @@
+// b200_gemm_grouped: C = A W^T (or A W) with the row bookkeeping that mixture-of-experts layers and per-head
+// (strided) projections need, beside linear.cu's plain b200_linear:
+//   * strided batches      : blockIdx.z = batch, A / W / C advance by element strides, rows have leading dimensions
+//                            (a head's slice of a wider activation is addressed in place, no copies)
+//   * groups               : blockIdx.z = group g owns rows [group_off[g], group_off[g+1]) of A and C and weight g
+//                            (the experts of a routed layer; the offsets live on the DEVICE, no host sync)
+//   * row gather           : A row r is a_rows[r] of the source (tokens sorted by expert are never materialised)
+//   * epilogues            : none | acc * sigmoid(aux) (output gate) | silu(acc_gate) * acc_up (GLU: the W tile holds
+//                            gate rows [0, N) and up rows [N, 2N) of the same features, the [M, 2N] intermediate is
+//                            never stored)
+// Element types: A and W float or bfloat16 (any mix), C float or bfloat16; accumulation is fp32 FMA in k order, so a
+// row's result does not depend on which other rows share the launch. Two kernels behind the entry point:
+//   gemm_grouped_mma_kernel  : bf16 operands (A converted on load), mma.sync m16n8k16, 64 x 64 x 32 tiles
+//   gemm_grouped_simt_kernel : every combination, true fp32 products (the float32 serving mode)
+#include <cuda_bf16.h>
+
+#include "b200_serve.h"
+#include "common.cuh"
+#include "launch_count.h"
+
+namespace b200 {
+
+struct GG {
+    const void* A; const void* W; void* C; const float* aux;
+    const int* a_rows; const int* group_off;
+    long long lda, ldw, ldc, ld_aux, sA, sW, sC, s_aux;
+    int M, N, K, epi;
+};
+
+constexpr int GBM = 64, GBN = 64, GBK = 16;
+
+template <typename TC>
+__device__ __forceinline__ void gg_store(const GG& g, TC* C, long long row, int col, float v, float v2, long long aux_off) {
+    if (g.epi == B200_GG_SIGMOID_MUL) v *= 1.f / (1.f + expf(-g.aux[aux_off + row * g.ld_aux + col]));
+    else if (g.epi == B200_GG_GLU) v = v / (1.f + expf(-v)) * v2;
+    C[row * g.ldc + col] = DT<TC>::from_f(v);
+}
+
+template <typename TA, typename TW, typename TC, bool TRANS_B, bool GLU>
+__global__ void __launch_bounds__(256) gemm_grouped_simt_kernel(GG g) {
+    __shared__ float As[GBK][GBM + 1];
+    __shared__ float Bs[GLU ? 2 : 1][GBK][GBN + 1];
+    const int z = blockIdx.z;
+    long long row0 = 0;
+    int M = g.M;
+    const TA* A = (const TA*)g.A;
+    const TW* W = (const TW*)g.W + (size_t)z * g.sW;
+    TC* C = (TC*)g.C;
+    long long aux_off = 0;
+    if (g.group_off) {
+        row0 = g.group_off[z];
+        M = g.group_off[z + 1] - (int)row0;
+    } else {
+        A += (size_t)z * g.sA;
+        C += (size_t)z * g.sC;
+        aux_off = (long long)z * g.s_aux;
+    }
+    const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+    if (m0 >= M) return;
+    const int N = g.N, K = g.K;
+    const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;
+    float acc[4][4], acc2[GLU ? 4 : 1][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; if (GLU) acc2[i][j] = 0.f; }
+    // the source row of each of the tile's 64 rows (gather), resolved once
+    __shared__ long long arow[GBM];
+    if (threadIdx.x < GBM) {
+        const int r = m0 + threadIdx.x;
+        long long src = -1;
+        if (r < M) src = g.a_rows ? (long long)g.a_rows[row0 + r] : row0 + r;
+        arow[threadIdx.x] = src;
+    }
+    __syncthreads();
+    for (int k0 = 0; k0 < K; k0 += GBK) {
+        for (int i = threadIdx.x; i < GBM * GBK; i += 256) {
+            const int r = i / GBK, kk = i - r * GBK;
+            const int gk = k0 + kk;
+            const long long src = arow[r];
+            As[kk][r] = (src >= 0 && gk < K) ? DT<TA>::to_f(A[src * g.lda + gk]) : 0.f;
+        }
+        if (TRANS_B) {
+            for (int i = threadIdx.x; i < GBN * GBK; i += 256) {
+                const int c = i / GBK, kk = i - c * GBK;
+                const int gn = n0 + c, gk = k0 + kk;
+                const bool ok = gn < N && gk < K;
+                Bs[0][kk][c] = ok ? DT<TW>::to_f(W[(long long)gn * g.ldw + gk]) : 0.f;
+                if (GLU) Bs[GLU ? 1 : 0][kk][c] = ok ? DT<TW>::to_f(W[(long long)(gn + N) * g.ldw + gk]) : 0.f;
+            }
+        } else {
+            for (int i = threadIdx.x; i < GBN * GBK; i += 256) {
+                const int kk = i / GBN, c = i - kk * GBN;
+                const int gn = n0 + c, gk = k0 + kk;
+                Bs[0][kk][c] = (gn < N && gk < K) ? DT<TW>::to_f(W[(long long)gk * g.ldw + gn]) : 0.f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < GBK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) b[j] = Bs[0][kk][tx * 4 + j];
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            if (GLU) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = Bs[GLU ? 1 : 0][kk][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) acc2[GLU ? i : 0][j] = fmaf(a[i], b[j], acc2[GLU ? i : 0][j]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = m0 + ty * 4 + i;
+        if (r >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = n0 + tx * 4 + j;
+            if (c >= N) continue;
+            gg_store<TC>(g, C, row0 + r, c, acc[i][j], GLU ? acc2[GLU ? i : 0][j] : 0.f, aux_off);
+        }
+    }
+}
+
+// ---- bf16 tensor-core tile: 64 x 64 x 32, 4 warps (2 x 2), each warp 32 x 32 = 2 m16 x 4 n8 fragments -----------
+constexpr int MBK = 32, MPAD = 8;   // smem rows of 40 bf16 (80 B): fragment loads hit distinct banks
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TA, typename TC, bool TRANS_B, bool GLU>
+__global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
+    using bf = __nv_bfloat16;
+    __shared__ __align__(16) bf As[GBM][MBK + MPAD];
+    __shared__ __align__(16) bf Bs[GLU ? 2 : 1][GBN][MBK + MPAD];   // [n][k] (k contiguous) whatever W's layout
+    __shared__ long long arow[GBM];
+    const int z = blockIdx.z;
+    long long row0 = 0;
+    int M = g.M;
+    const TA* A = (const TA*)g.A;
+    const bf* W = (const bf*)g.W + (size_t)z * g.sW;
+    TC* C = (TC*)g.C;
+    long long aux_off = 0;
+    if (g.group_off) {
+        row0 = g.group_off[z];
+        M = g.group_off[z + 1] - (int)row0;
+    } else {
+        A += (size_t)z * g.sA;
+        C += (size_t)z * g.sC;
+        aux_off = (long long)z * g.s_aux;
+    }
+    const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+    if (m0 >= M) return;
+    const int N = g.N, K = g.K;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int wm = (warp / 2) * 32, wn = (warp % 2) * 32;
+    const int gid = lane / 4, tig = lane % 4;
+    float acc[2][4][4], acc2[GLU ? 2 : 1][4][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { acc[i][j][k] = 0.f; if (GLU) acc2[i][j][k] = 0.f; }
+    if (threadIdx.x < GBM) {
+        const int r = m0 + threadIdx.x;
+        long long src = -1;
+        if (r < M) src = g.a_rows ? (long long)g.a_rows[row0 + r] : row0 + r;
+        arow[threadIdx.x] = src;
+    }
+    __syncthreads();
+    for (int k0 = 0; k0 < K; k0 += MBK) {
+        for (int i = threadIdx.x; i < GBM * MBK; i += 128) {
+            const int r = i / MBK, kk = i - r * MBK;
+            const int gk = k0 + kk;
+            const long long src = arow[r];
+            As[r][kk] = (src >= 0 && gk < K) ? __float2bfloat16_rn(DT<TA>::to_f(A[src * g.lda + gk])) : __float2bfloat16_rn(0.f);
+        }
+        if (TRANS_B) {
+            for (int i = threadIdx.x; i < GBN * MBK; i += 128) {
+                const int c = i / MBK, kk = i - c * MBK;
+                const int gn = n0 + c, gk = k0 + kk;
+                const bool ok = gn < N && gk < K;
+                Bs[0][c][kk] = ok ? W[(long long)gn * g.ldw + gk] : __float2bfloat16_rn(0.f);
+                if (GLU) Bs[GLU ? 1 : 0][c][kk] = ok ? W[(long long)(gn + N) * g.ldw + gk] : __float2bfloat16_rn(0.f);
+            }
+        } else {
+            for (int i = threadIdx.x; i < GBN * MBK; i += 128) {
+                const int kk = i / GBN, c = i - kk * GBN;
+                const int gn = n0 + c, gk = k0 + kk;
+                Bs[0][c][kk] = (gn < N && gk < K) ? W[(long long)gk * g.ldw + gn] : __float2bfloat16_rn(0.f);
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < MBK; ks += 16) {
+            uint32_t a[2][4];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int r = wm + i * 16 + gid;
+                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][ks + tig * 2]);
+                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + tig * 2]);
+                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 8 + tig * 2]);
+                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 8 + tig * 2]);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = wn + j * 8 + gid;
+                uint32_t b[2];
+                b[0] = *reinterpret_cast<const uint32_t*>(&Bs[0][c][ks + tig * 2]);
+                b[1] = *reinterpret_cast<const uint32_t*>(&Bs[0][c][ks + 8 + tig * 2]);
+                mma_bf16(acc[0][j], a[0], b);
+                mma_bf16(acc[1][j], a[1], b);
+                if (GLU) {
+                    b[0] = *reinterpret_cast<const uint32_t*>(&Bs[GLU ? 1 : 0][c][ks + tig * 2]);
+                    b[1] = *reinterpret_cast<const uint32_t*>(&Bs[GLU ? 1 : 0][c][ks + 8 + tig * 2]);
+                    mma_bf16(acc2[0][j], a[0], b);
+                    mma_bf16(acc2[GLU ? 1 : 0][j], a[1], b);
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int r = m0 + wm + i * 16 + gid + (k / 2) * 8;
+                const int c = n0 + wn + j * 8 + tig * 2 + (k % 2);
+                if (r < M && c < N)
+                    gg_store<TC>(g, C, row0 + r, c, acc[i][j][k], GLU ? acc2[GLU ? i : 0][j][k] : 0.f, aux_off);
+            }
+}
+
+template <typename TA, typename TW, typename TC>
+static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
+    if (g.epi == B200_GG_GLU) {
+        if (!trans_b) return B200_EUNSUPPORTED;
+        gemm_grouped_simt_kernel<TA, TW, TC, true, true><<<grid, 256, 0, s>>>(g);
+    } else if (trans_b)
+        gemm_grouped_simt_kernel<TA, TW, TC, true, false><<<grid, 256, 0, s>>>(g);
+    else
+        gemm_grouped_simt_kernel<TA, TW, TC, false, false><<<grid, 256, 0, s>>>(g);
+    return (int)cudaGetLastError();
+}
+template <typename TA, typename TC>
+static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
+    if (g.epi == B200_GG_GLU) {
+        if (!trans_b) return B200_EUNSUPPORTED;
+        gemm_grouped_mma_kernel<TA, TC, true, true><<<grid, 128, 0, s>>>(g);
+    } else if (trans_b)
+        gemm_grouped_mma_kernel<TA, TC, true, false><<<grid, 128, 0, s>>>(g);
+    else
+        gemm_grouped_mma_kernel<TA, TC, false, false><<<grid, 128, 0, s>>>(g);
+    return (int)cudaGetLastError();
+}
+
+static bool mma_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200_GG_SIMT");   // 1: bf16 operands on the SIMT kernel too (debugging aid)
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemm_grouped(const b200_gemm_grouped_args* p, void* stream) {
+    if (!p || !p->A || !p->W || !p->C || p->N <= 0 || p->K <= 0 || p->M < 0 || p->batch < 1) return B200_EINVAL;
+    if (p->M == 0) return B200_OK;
+    if (p->epi == B200_GG_SIGMOID_MUL && !p->aux) return B200_EINVAL;
+    GG g;
+    g.A = p->A; g.W = p->W; g.C = p->C; g.aux = p->aux; g.a_rows = p->a_rows; g.group_off = p->group_off;
+    g.lda = p->lda; g.ldw = p->ldw; g.ldc = p->ldc; g.ld_aux = p->ld_aux;
+    g.sA = p->stride_a; g.sW = p->stride_w; g.sC = p->stride_c; g.s_aux = p->stride_aux;
+    g.M = p->M; g.N = p->N; g.K = p->K; g.epi = p->epi;
+    // groups: M is the largest number of rows one group can own (the grid covers it; CTAs beyond a group's rows leave)
+    dim3 grid((p->N + GBN - 1) / GBN, (p->M + GBM - 1) / GBM, p->batch);
+    if (grid.y > 65535 || grid.z > 65535) return B200_EUNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool tb = p->trans_b != 0;
+    using bf = __nv_bfloat16;
+    const int ta = p->a_dtype, tw = p->w_dtype, tc = p->c_dtype;
+    int rc = B200_EUNSUPPORTED;
+    if (tw == B200_BF16 && mma_enabled()) {
+        if (ta == B200_BF16 && tc == B200_F32) rc = gg_launch_mma<bf, float>(g, grid, tb, s);
+        else if (ta == B200_BF16 && tc == B200_BF16) rc = gg_launch_mma<bf, bf>(g, grid, tb, s);
+        else if (ta == B200_F32 && tc == B200_F32) rc = gg_launch_mma<float, float>(g, grid, tb, s);
+        else if (ta == B200_F32 && tc == B200_BF16) rc = gg_launch_mma<float, bf>(g, grid, tb, s);
+    } else if (tw == B200_BF16) {
+        if (ta == B200_BF16 && tc == B200_F32) rc = gg_launch_simt<bf, bf, float>(g, grid, tb, s);
+        else if (ta == B200_BF16 && tc == B200_BF16) rc = gg_launch_simt<bf, bf, bf>(g, grid, tb, s);
+        else if (ta == B200_F32 && tc == B200_F32) rc = gg_launch_simt<float, bf, float>(g, grid, tb, s);
+        else if (ta == B200_F32 && tc == B200_BF16) rc = gg_launch_simt<float, bf, bf>(g, grid, tb, s);
+    } else if (tw == B200_F32 && ta == B200_F32 && tc == B200_F32) {
+        rc = gg_launch_simt<float, float, float>(g, grid, tb, s);
+    }
+    if (rc == 0) count_launch();
+    return rc;
+}

@@ -1,0 +1,85 @@
+// Model families behind b200_serve.h: the interface a family implements, the registry that maps config.json's
+// "architecture" to a factory, and the batch bookkeeping every family shares (sequence slots, their lengths, the page
+// pool of their cache, the per-token slot / position / row tables of a step).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "b200_serve.h"
+#include "json_min.h"
+#include "page_pool.h"
+
+namespace b200 {
+
+struct StepEntry {
+    int slot;
+    int n_tokens;
+    const int* tokens;
+    int n_want;
+    const int* want;   // indices into this entry's tokens
+};
+
+struct ModelDir {
+    std::string path;
+    Json config;
+};
+
+// Sequence slots over one PagePool, plus the device tables of a step: for token t of the packed batch its id, slot and
+// position, and for every wanted place its row in the batch. Filled on the host (pinned), uploaded with one copy.
+class SequenceBatch {
+public:
+    ~SequenceBatch();
+    // page_rows rows per page; the pool holds ceil(max_tokens / page_rows) pages (each sequence rounds up to whole pages)
+    int init(int max_tokens, int page_rows, int n_slots, int max_positions, std::string& err);
+    // Validates the entries, takes pages, advances the slots' lengths and uploads the tables on `stream`.
+    // On failure nothing has changed (B200_ENOMEM: the pool cannot hold the step).
+    int begin_step(const std::vector<StepEntry>& entries, cudaStream_t stream, std::string& err);
+    int release(int slot);
+
+    PagePool pool;
+    int n_slots = 0, max_positions = 0;
+    std::vector<int> length;      // tokens cached per slot
+    // the step prepared by begin_step
+    int n_tokens = 0, n_want = 0;
+    const int* d_ids() const { return dev_; }
+    const int* d_slot() const { return dev_ + cap_; }
+    const int* d_pos() const { return dev_ + 2 * (size_t)cap_; }
+    const int* d_want_rows() const { return dev_ + 3 * (size_t)cap_; }
+
+private:
+    int ensure_capacity(int tokens);
+    int* host_ = nullptr;   // pinned [4, cap]
+    int* dev_ = nullptr;
+    int cap_ = 0;
+    cudaEvent_t copied_ = nullptr;   // the upload out of host_ has run (host_ may be rewritten)
+};
+
+class Model {
+public:
+    virtual ~Model() {}
+    virtual const char* family() const = 0;
+    virtual int vocab() const = 0;
+    virtual int width() const = 0;
+    virtual int layer_count() const = 0;
+    virtual SequenceBatch& sequences() = 0;
+    // entries as ONE batch; logits_out host fp32 [sum n_want, vocab] and ids_out host [sum n_want] may be NULL
+    virtual int step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) = 0;
+    virtual int release(int slot) = 0;
+    virtual int capture_layers(int) { return B200_EUNSUPPORTED; }
+    virtual int captured_layers(float*, size_t) { return B200_EUNSUPPORTED; }
+    virtual int step_launches() const { return 0; }
+};
+
+using ModelFactory = Model* (*)(const ModelDir& dir, const b200_model_options& opt, std::string& err);
+// static registration: one FamilyRegistrar object per family, in the family's own translation unit
+struct FamilyRegistrar {
+    FamilyRegistrar(const char* architecture, ModelFactory factory);
+};
+
+// Continuous-batching greedy generation over any Model (b200_model_generate)
+int generate_greedy(Model& m, int n_requests, const int* prompt_ids, const int* lens, int max_new, int eos_id, int chunk,
+                    int* out_ids, int* n_generated, std::string& err);
+
+}  // namespace b200

@@ -1,0 +1,165 @@
+"""ctypes plumbing for ``include/b200_serve.h``: the model-family layer (registry, step function, paged sequence
+cache, continuous-batching scheduler) and the kernels it brings. Tests and the bench call the library through this
+module; the product path is the C ABI itself and ``bin/b200_serve``."""
+import ctypes as C
+
+import numpy as np
+
+from . import capi
+
+F32, BF16 = 0, 2
+GG_NONE, GG_SIGMOID_MUL, GG_GLU = 0, 1, 2
+_vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
+
+
+class GemmGroupedArgs(C.Structure):
+    """mirror of ``b200_gemm_grouped_args``"""
+    _fields_ = [("A", _vp), ("W", _vp), ("C", _vp), ("aux", _vp), ("a_rows", _vp), ("group_off", _vp),
+                ("lda", _ll), ("ldw", _ll), ("ldc", _ll), ("ld_aux", _ll),
+                ("stride_a", _ll), ("stride_w", _ll), ("stride_c", _ll), ("stride_aux", _ll),
+                ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("trans_b", _i), ("epi", _i),
+                ("a_dtype", _i), ("w_dtype", _i), ("c_dtype", _i)]
+
+
+class ModelOptions(C.Structure):
+    """mirror of ``b200_model_options``"""
+    _fields_ = [("dtype", _i), ("max_tokens", _i), ("max_slots", _i), ("max_step_tokens", _i)]
+
+
+_ip = C.POINTER(C.c_int)
+SERVE_PROTOTYPES = {
+    "b200_embed_positions": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_layernorm_pair": (_i, [_vp, _vp, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "b200_gemm_grouped": (_i, [C.POINTER(GemmGroupedArgs), _vp]),
+    "b200_latent_store": (_i, [_vp, _ll, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_latent_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp]),
+    "b200_moe_route": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
+    "b200_moe_dispatch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
+    "b200_residual_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "b200_serve_last_error": (C.c_char_p, []),
+    "b200_model_families": (C.c_char_p, []),
+    "b200_model_open": (_vp, [C.c_char_p, C.POINTER(ModelOptions)]),
+    "b200_model_close": (None, [_vp]),
+    "b200_model_family": (C.c_char_p, [_vp]),
+    "b200_model_vocab": (_i, [_vp]),
+    "b200_model_width": (_i, [_vp]),
+    "b200_model_layer_count": (_i, [_vp]),
+    "b200_model_max_positions": (_i, [_vp]),
+    "b200_model_page_rows": (_i, [_vp]),
+    "b200_model_pages_total": (_i, [_vp]),
+    "b200_model_pages_free": (_i, [_vp]),
+    "b200_model_slot_length": (_i, [_vp, _i]),
+    "b200_model_slot_pages": (_i, [_vp, _i, _vp, _i]),
+    "b200_model_step": (_i, [_vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "b200_model_release": (_i, [_vp, _i]),
+    "b200_model_capture_layers": (_i, [_vp, _i]),
+    "b200_model_captured_layers": (_i, [_vp, _vp, _sz]),
+    "b200_model_step_launches": (_i, [_vp]),
+    "b200_model_generate": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "b200_session_create": (_vp, [_vp]),
+    "b200_session_destroy": (None, [_vp]),
+    "b200_session_slot": (_i, [_vp, C.c_char_p]),
+    "b200_session_end": (_i, [_vp, C.c_char_p]),
+}
+
+_bound = False
+
+
+def lib():
+    global _bound
+    handle = capi.lib()
+    if not _bound:
+        for name, (res, args) in SERVE_PROTOTYPES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _bound = True
+    return handle
+
+
+def last_error():
+    return lib().b200_serve_last_error().decode()
+
+
+def _ints(a):
+    a = np.ascontiguousarray(np.asarray(a, dtype=np.int32))
+    return a, a.ctypes.data_as(_vp)
+
+
+class Model:
+    """A checkpoint folder opened through the registry (``b200_model_open``)."""
+
+    def __init__(self, folder, dtype=BF16, max_tokens=1024, max_slots=4):
+        opt = ModelOptions(dtype, max_tokens, max_slots, 0)
+        self._h = lib().b200_model_open(str(folder).encode(), C.byref(opt))
+        if not self._h:
+            raise RuntimeError("[b200][ERROR] model_open: " + last_error())
+        L = lib()
+        self.family = L.b200_model_family(self._h).decode()
+        self.vocab, self.width = L.b200_model_vocab(self._h), L.b200_model_width(self._h)
+        self.n_layers, self.page_rows = L.b200_model_layer_count(self._h), L.b200_model_page_rows(self._h)
+        self.pages_total = L.b200_model_pages_total(self._h)
+
+    def close(self):
+        if self._h:
+            lib().b200_model_close(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    @property
+    def pages_free(self):
+        return lib().b200_model_pages_free(self._h)
+
+    def slot_length(self, slot):
+        return lib().b200_model_slot_length(self._h, slot)
+
+    def slot_pages(self, slot):
+        buf = np.zeros(4096, np.int32)
+        n = lib().b200_model_slot_pages(self._h, slot, buf.ctypes.data_as(_vp), len(buf))
+        return buf[:n].tolist()
+
+    def step(self, entries, logits=True, ids=False):
+        """entries: list of (slot, tokens, want). Returns logits [sum want, vocab] (and greedy ids when ids=True)."""
+        slots, _s = _ints([e[0] for e in entries])
+        counts, _c = _ints([len(e[1]) for e in entries])
+        toks, _t = _ints([t for e in entries for t in e[1]] or [0])
+        nw, _nw = _ints([len(e[2]) for e in entries])
+        want, _w = _ints([w for e in entries for w in e[2]] or [0])
+        total = int(nw.sum())
+        out = np.zeros((max(total, 1), self.vocab), np.float32)
+        picks = np.zeros(max(total, 1), np.int32)
+        rc = lib().b200_model_step(self._h, len(entries), _s, _c, _t, _nw, _w,
+                                   out.ctypes.data_as(_vp) if logits else None, picks.ctypes.data_as(_vp) if ids else None)
+        if rc != 0:
+            raise RuntimeError(f"[b200][ERROR] model_step rc={rc}: {last_error()}")
+        return (out[:total], picks[:total]) if ids else out[:total]
+
+    def release(self, slot):
+        return lib().b200_model_release(self._h, slot)
+
+    def capture_layers(self, on=True):
+        lib().b200_model_capture_layers(self._h, int(on))
+
+    def captured_layers(self, n_tokens):
+        out = np.zeros((self.n_layers, n_tokens, self.width), np.float32)
+        rc = lib().b200_model_captured_layers(self._h, out.ctypes.data_as(_vp), out.size)
+        if rc != n_tokens:
+            raise RuntimeError(f"[b200][ERROR] captured_layers rc={rc}")
+        return out
+
+    @property
+    def step_launches(self):
+        return lib().b200_model_step_launches(self._h)
+
+    def generate(self, prompts, max_new, eos_id=-1, chunk=0):
+        ids, _p = _ints([t for p in prompts for t in p])
+        lens, _l = _ints([len(p) for p in prompts])
+        out = np.zeros((len(prompts), max_new), np.int32)
+        made = np.zeros(len(prompts), np.int32)
+        rc = lib().b200_model_generate(self._h, len(prompts), _p, _l, max_new, eos_id, chunk, out.ctypes.data_as(_vp),
+                                       made.ctypes.data_as(_vp))
+        if rc < 0:
+            raise RuntimeError(f"[b200][ERROR] model_generate rc={rc}: {last_error()}")
+        return [out[i, :made[i]].tolist() for i in range(len(prompts))], rc

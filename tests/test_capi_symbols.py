@@ -11,7 +11,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_symbols():
     names = set()
-    for hdr in ("b200_llama.h", "b200_engine.h"):
+    for hdr in ("b200_llama.h", "b200_engine.h", "b200_serve.h"):
         text = open(os.path.join(ROOT, "include", hdr)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names |= set(re.findall(r"\b(b200_\w+)\s*\(", text))
@@ -40,7 +40,7 @@ def test_library_exports_every_declared_symbol(pkg):
 
 
 def test_prototype_table_matches_header(pkg):
-    assert sorted(list(pkg.capi.PROTOTYPES) + list(pkg.engine.ENGINE_PROTOTYPES)) == declared_symbols()
+    assert sorted(list(pkg.capi.PROTOTYPES) + list(pkg.engine.ENGINE_PROTOTYPES) + list(pkg.serve.SERVE_PROTOTYPES)) == declared_symbols()
 
 
 def test_ops_fail_loudly_without_cuda(pkg):
