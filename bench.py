@@ -44,7 +44,10 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "nekodra"])
+    ap.add_argument("--size", default="m", choices=["s", "m"],
+                    help="nekodra: model shape (llm-inference_b200/bench_families.py SIZES)")
+    ap.add_argument("--prompt", type=int, default=2048, help="nekodra: prompt tokens of the prefill measurement")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="cfg5: fused one-shot NVLink allreduce (product) or ncclAllReduce + AddResidual (baseline)")
     ap.add_argument("--batch", type=int, default=None)
@@ -898,8 +901,22 @@ def extras_multi_gpu(pkg, args, rank, world, local_rank, peak):
 # --------------------------------------------------------------------------------------------
 # the B200 arm
 # --------------------------------------------------------------------------------------------
+def bench_family(args):
+    """--workload nekodra: prefill and decode tokens/s of the Nekodra family (include/b200_serve.h) beside the LLaMA engine
+    at equal size; one JSON line of its own shape (the default workload's line and contract are untouched)."""
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from llm_inference_b200 import bench_families
+    res = bench_families.run(pkg, size=args.size, prompt=args.prompt, batch=args.batch or 8, context=args.context or 1024,
+                             steps=min(args.steps, 20), warmup=max(args.warmup, 3))
+    res["gpu_launches"] = int(pkg.capi.lib().b200_launch_count())
+    print(json.dumps(res))
+
+
 def main():
     args = parse()
+    if args.workload == "nekodra":
+        return bench_family(args)
     wl = workload(args)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -1,0 +1,92 @@
+"""Prefill and decode throughput of a model family served through include/b200_serve.h, beside the LLaMA engine at
+equal size (same width, heads, layers, vocabulary and the same feed-forward width per token), random weights.
+Called by bench.py --workload nekodra; prints one JSON line."""
+import json
+import os
+import tempfile
+import time
+
+SIZES = {
+    # width, heads, dim, vdim, kv_rank, experts, ff, top, identity, shared_ff, layers, vocab
+    "s": dict(width=1024, heads=8, dim=128, vdim=128, kv_rank=256, experts=8, ff=512, top=2, identity=2, shared_ff=1024,
+              n_layers=4, vocab=32000),
+    "m": dict(width=2048, heads=16, dim=128, vdim=128, kv_rank=512, experts=16, ff=1024, top=4, identity=2, shared_ff=2048,
+              n_layers=4, vocab=32000),
+}
+
+
+def timed(fn, steps, warmup):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / steps
+
+
+def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, dtype="bfloat16"):
+    import numpy as np
+    import torch
+
+    S, E, capi = pkg.serve, pkg.engine, pkg.capi
+    sz = SIZES[size]
+    rng = np.random.default_rng(0)
+    out = {"workload": "nekodra", "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
+           "dtype": dtype, "data": "synthetic ids, random weights", "timing": "host clock around synchronous steps (each step ends "
+           "with the device-to-host copy of its results), after warm-up"}
+    with tempfile.TemporaryDirectory() as folder:
+        cfg, w = S.random_nekodra(max_positions=max(prompt, context + steps + warmup + 8) + 64, **sz)
+        S.write_checkpoint(folder, cfg, w)
+        del w
+        PR = 64
+        need = max(prompt + PR, batch * (context + steps + warmup + PR + 8))
+        m = S.Model(folder, dtype=S.BF16 if dtype == "bfloat16" else S.F32, max_tokens=need, max_slots=batch)
+    V = sz["vocab"]
+    ids = rng.integers(0, V, prompt).tolist()
+
+    def prefill():
+        m.step([(0, ids, [prompt - 1])], logits=False, ids=True)
+        m.release(0)
+    t = timed(prefill, steps, warmup)
+    out["prefill"] = {"tokens_per_s": prompt / t, "ms": t * 1e3, "launches": m.step_launches}
+    for b in range(batch):
+        m.step([(b, rng.integers(0, V, context).tolist(), [])], logits=False)
+    tok = rng.integers(0, V, batch).tolist()
+
+    def decode():
+        m.step([(b, [tok[b]], [0]) for b in range(batch)], logits=False, ids=True)
+    t = timed(decode, steps, warmup)
+    out["decode"] = {"tokens_per_s": batch / t, "ms": t * 1e3, "launches": m.step_launches}
+    m.close()
+
+    # the closest existing model: the LLaMA engine with the same width, heads, layers and vocabulary, and the
+    # feed-forward width a Nekodra token actually uses (its chosen experts + the shared one); fp16
+    inter = sz["top"] * sz["ff"] + sz["shared_ff"]
+    shape = dict(num_layers=sz["n_layers"], head_num=sz["heads"], kv_head_num=sz["heads"], head_size=sz["dim"], inter_size=inter,
+                 vocab_size=V)
+    ll = {"shape": shape, "dtype": "fp16"}
+    try:
+        eng = E.Engine(1, prompt + 8, dtype=capi.F16, **shape)
+        eng.init_random(seed=1, std=0.02)
+        pid = rng.integers(0, V, (1, prompt)).astype(np.int32)
+
+        def ll_prefill():
+            eng.reset()
+            eng.prefill(pid)
+        t = timed(ll_prefill, steps, warmup)
+        ll["prefill"] = {"tokens_per_s": prompt / t, "ms": t * 1e3}
+        eng.close()
+        eng = E.Engine(batch, context + steps + warmup + 16, dtype=capi.F16, **shape)
+        eng.init_random(seed=1, std=0.02)
+        eng.fill_kv_random(context, seed=2, amp=0.5)
+        did = rng.integers(0, V, batch).astype(np.int32)
+        t = timed(lambda: eng.decode_step_host(did), steps, warmup)
+        ll["decode"] = {"tokens_per_s": batch / t, "ms": t * 1e3, "launches": eng.launches_per_step}
+        eng.close()
+    except Exception as ex:   # the comparison must not take the family's own numbers down
+        ll["failed"] = f"{type(ex).__name__}: {ex}"
+    out["llama_equal_size"] = ll
+    return out

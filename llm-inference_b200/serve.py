@@ -163,3 +163,69 @@ class Model:
         if rc < 0:
             raise RuntimeError(f"[b200][ERROR] model_generate rc={rc}: {last_error()}")
         return [out[i, :made[i]].tolist() for i in range(len(prompts))], rc
+
+
+def write_checkpoint(folder, config, tensors):
+    """config.json + model.safetensors (bfloat16) from a dict name -> torch tensor: random-weight models for the bench
+    and for trying a configuration out."""
+    import json
+    import os
+    import struct
+
+    import torch
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(config, f)
+    header, off = {}, 0
+    for name, t in tensors.items():
+        n = t.numel() * 2
+        header[name] = dict(dtype="BF16", shape=list(t.shape), data_offsets=[off, off + n])
+        off += n
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for t in tensors.values():
+            f.write(t.to(torch.bfloat16).contiguous().view(torch.int16).numpy().tobytes())
+
+
+def random_nekodra(width, heads, dim, vdim, kv_rank, experts, ff, top, identity, shared_ff, n_layers, vocab, max_positions,
+                   share_every=2, seed=0):
+    """(config, tensors) of a random Nekodra model; every `share_every`-th layer reads the previous layer's cached rows"""
+    import math
+
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16)
+
+    cfg = dict(architecture="Nekodra", vocab=vocab, width=width, max_positions=max_positions, norm=dict(eps=1e-5), layers=[])
+    w = {"embed": rnd(vocab, width, s=1.0), "pos": rnd(max_positions, width, s=0.3), "head": rnd(vocab, width),
+         "final.norm": torch.ones(width), "final.norm.b": torch.zeros(width)}
+    for i in range(n_layers):
+        pre = f"l{i}."
+        mx = dict(heads=heads, dim=dim, vdim=vdim, kv_rank=kv_rank, scale=1.0 / math.sqrt(dim))
+        shares = share_every > 0 and i % share_every == share_every - 1 and i > 0
+        for n in ("norm1", "norm2"):
+            w[pre + n], w[pre + n + ".b"] = torch.ones(width), torch.zeros(width)
+        w[pre + "mix.q"], w[pre + "mix.g"] = rnd(heads * dim, width), rnd(heads * vdim, width)
+        if shares:
+            mx["kv_from"] = i - 1
+        else:
+            w[pre + "mix.dkv"], w[pre + "mix.dkv.norm"] = rnd(kv_rank, width), torch.ones(kv_rank)
+        w[pre + "mix.uk"], w[pre + "mix.uv"] = rnd(heads * dim, kv_rank), rnd(heads * vdim, kv_rank)
+        w[pre + "mix.sink"], w[pre + "mix.o"] = torch.zeros(heads), rnd(width, heads * vdim)
+        for e in range(experts):
+            w[pre + f"mlp.e{e}.gate"], w[pre + f"mlp.e{e}.up"] = rnd(ff, width), rnd(ff, width)
+            w[pre + f"mlp.e{e}.down"] = rnd(width, ff)
+        w[pre + "mlp.router"], w[pre + "mlp.correction"] = rnd(experts + identity, width), torch.zeros(experts + identity)
+        w[pre + "mlp.shared.gate"], w[pre + "mlp.shared.up"] = rnd(shared_ff, width), rnd(shared_ff, width)
+        w[pre + "mlp.shared.down"] = rnd(width, shared_ff)
+        cfg["layers"].append(dict(type="latent_attention", mixer=mx,
+                                  mlp=dict(kind="moe", expert=dict(ff=ff), shared=dict(ff=shared_ff),
+                                           router=dict(experts=experts, identity=identity, top=top, scale=1.0))))
+    return cfg, w
