@@ -57,6 +57,15 @@ typedef struct b200_gemm_grouped_args {
 } b200_gemm_grouped_args;
 int b200_gemm_grouped(const b200_gemm_grouped_args* args, void* stream);
 
+/* y[n_tokens, N] = x[n_tokens, K] W[N, K]^T for contiguous operands (epi B200_GG_NONE), or the GLU form with W [2N, K]
+ * (B200_GG_GLU). bfloat16 operands run on the tcgen05 / TMEM GEMM of the LLaMA path (weights streamed once through the
+ * M axis up to 256 token rows, tokens on the M axis above; fp32 accumulation; out_dtype B200_BF16 or B200_F32) when the
+ * shape allows (K % 8 == 0, 16-byte aligned pointers, GLU: N % 128 == 0); everything else, and B200_F32 operands, goes
+ * to b200_gemm_grouped. workspace: split-K partials of the weight-streaming mode (may be NULL: single split). */
+size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K);
+int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
 /* Latent cache rows: for token t, row = raw[t, 0:rank] (fp32, leading dimension ld_raw) divided by its root mean
  * square (eps inside the root) times w, stored as `dtype` at position pos[t] of sequence slot[t]:
  * pool[(pages[slot[t] * max_pages + pos[t] / page_rows] * page_rows + pos[t] % page_rows) * rank + :]. */

@@ -269,6 +269,10 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     return (int)cudaGetLastError();
 }
 
+int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, bool glu, void* workspace,
+                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu
+size_t gemm_tcgen05_ex_workspace_bytes(int M, int N, int K);
+
 static bool mma_enabled() {
     static int v = -1;
     if (v < 0) {
@@ -314,4 +318,25 @@ extern "C" int b200_gemm_grouped(const b200_gemm_grouped_args* p, void* stream) 
     }
     if (rc == 0) count_launch();
     return rc;
+}
+
+extern "C" size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K) {
+    return n_tokens > 0 && N > 0 && K > 0 ? gemm_tcgen05_ex_workspace_bytes(n_tokens, N, K) : 0;
+}
+
+extern "C" int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
+                              void* workspace, size_t workspace_bytes, void* stream) {
+    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU)) return B200_EINVAL;
+    if (n_tokens == 0) return B200_OK;
+    if (in_dtype == B200_BF16 && (out_dtype == B200_BF16 || out_dtype == B200_F32)) {
+        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU, workspace,
+                                       workspace_bytes, (cudaStream_t)stream);
+        if (rc != B200_EUNSUPPORTED) return rc;
+    }
+    b200_gemm_grouped_args g{};
+    g.A = x; g.W = W; g.C = y;
+    g.lda = K; g.ldw = K; g.ldc = N;
+    g.M = n_tokens; g.N = N; g.K = K; g.batch = 1; g.trans_b = 1; g.epi = epi;
+    g.a_dtype = in_dtype; g.w_dtype = in_dtype; g.c_dtype = out_dtype;
+    return b200_gemm_grouped(&g, stream);
 }

@@ -42,6 +42,8 @@ struct GemmParams {
     int ldc;            // = N_out
     int tokens;
     int m_tiles, n_tiles, splits, k_blocks;
+    int in_bf16;        // operands are bfloat16 instead of fp16 (same tiles, other instruction descriptor)
+    int out_kind;       // element type of C: 0 fp16 (rounding points of the reference sequence), 1 bfloat16, 2 fp32
 };
 
 template <int BN>
@@ -52,6 +54,29 @@ struct GemmSmem {
     static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
     static constexpr int kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;                // two accumulator stages
 };
+
+// stores of the epilogue in the element type GemmParams::out_kind names (idx in elements)
+__device__ __forceinline__ void store8(void* C, size_t idx, const float (&f)[8], int kind) {
+    if (kind == 0) st16(reinterpret_cast<__half*>(C) + idx, Unpack<__half>::put(f));
+    else if (kind == 1) {
+        Pack16 v;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            v.w[i] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+        st16(reinterpret_cast<__nv_bfloat16*>(C) + idx, v);
+    } else {
+        float* d = reinterpret_cast<float*>(C) + idx;
+        *reinterpret_cast<float4*>(d) = make_float4(f[0], f[1], f[2], f[3]);
+        *reinterpret_cast<float4*>(d + 4) = make_float4(f[4], f[5], f[6], f[7]);
+    }
+}
+__device__ __forceinline__ void store1(void* C, size_t idx, float f, int kind) {
+    if (kind == 0) reinterpret_cast<__half*>(C)[idx] = __float2half_rn(f);
+    else if (kind == 1) reinterpret_cast<__nv_bfloat16*>(C)[idx] = __float2bfloat16_rn(f);
+    else reinterpret_cast<float*>(C)[idx] = f;
+}
 
 // GLU (normal mode, BN = 256): W = [2*inter, K] with gate rows first (act_kernel.cu:28-29). The B tile of
 // feature tile nt is 128 gate rows (nt*128) followed by the matching 128 up rows (inter + nt*128), so the
@@ -126,7 +151,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
-        constexpr uint32_t idesc = make_idesc_f16(kBM, BN);
+        // bfloat16 operands: A format (bits [7,10)) and B format (bits [10,13)) = 1
+        const uint32_t idesc = make_idesc_f16(kBM, BN) | (p.in_bf16 ? ((1u << 7) | (1u << 10)) : 0u);
         int stage = 0;
         uint32_t phase = 0;
         int acc = 0;
@@ -164,7 +190,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;   // TMEM lanes [32*quarter, 32*quarter + 32) belong to this warp
         int acc = 0;
         uint32_t acc_phase = 0;
-        __half* C = reinterpret_cast<__half*>(p.C);
+        void* const C = p.C;
+        const int ok = p.out_kind;
         const __half* bias = reinterpret_cast<const __half*>(p.bias);
         for (int u = blockIdx.x; u < units; u += gridDim.x) {
             const int mt = u % p.m_tiles, rest = u / p.m_tiles;
@@ -183,18 +210,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     tmem_ld_32x32(taddr + (uint32_t)(128 + c0), u);
                     const int col0 = nt * 128 + c0;
                     if (row < p.tokens && col0 < p.rows_b) {
-                        __half* dst = C + (size_t)row * p.ldc + col0;
+                        const size_t dst = (size_t)row * p.ldc + col0;
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
                             float f[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
-                                const float gv = __half2float(__float2half_rn(__uint_as_float(g[q * 8 + e])));
-                                const float uv = __half2float(__float2half_rn(__uint_as_float(u[q * 8 + e])));
-                                const float sv = __half2float(__float2half_rn(gv / (1.f + expf(-gv))));
-                                f[e] = sv * uv;
+                                float gv = __uint_as_float(g[q * 8 + e]), uv = __uint_as_float(u[q * 8 + e]);
+                                if (ok == 0) {   // fp16: the rounding points of the unfused sequence
+                                    gv = __half2float(__float2half_rn(gv));
+                                    uv = __half2float(__float2half_rn(uv));
+                                    f[e] = __half2float(__float2half_rn(gv / (1.f + expf(-gv)))) * uv;
+                                } else
+                                    f[e] = gv / (1.f + expf(-gv)) * uv;
                             }
-                            if (col0 + q * 8 + 8 <= p.rows_b) st16(dst + q * 8, Unpack<__half>::put(f));
+                            if (col0 + q * 8 + 8 <= p.rows_b) store8(C, dst + q * 8, f, ok);
                         }
                     }
                 }
@@ -207,7 +237,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!SWAP) {
                     // row = token, col = output feature: 32 consecutive features per thread
                     if (row < p.tokens && col0 < p.rows_b) {
-                        __half* dst = C + (size_t)row * p.ldc + col0;
+                        const size_t dst = (size_t)row * p.ldc + col0;
                         if (col0 + 32 <= p.rows_b && (p.ldc & 7) == 0) {
 #pragma unroll
                             for (int q = 0; q < 4; ++q) {
@@ -217,7 +247,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                     f[e] = __uint_as_float(v[q * 8 + e]);
                                     if (bias) f[e] += __half2float(bias[col0 + q * 8 + e]);
                                 }
-                                st16(dst + q * 8, Unpack<__half>::put(f));
+                                store8(C, dst + q * 8, f, ok);
                             }
                         } else {
                             // unrolled with a predicate: a run-time index would move v[] to local memory (no L1 behind
@@ -227,7 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (col0 + j >= p.rows_b) continue;
                                 float f = __uint_as_float(v[j]);
                                 if (bias) f += __half2float(bias[col0 + j]);
-                                dst[j] = __float2half_rn(f);
+                                store1(C, dst + j, f, ok);
                             }
                         }
                     }
@@ -243,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                                 if (p.partial)
                                     p.partial[((size_t)sp * p.tokens + tok) * p.ldc + row] = f;
                                 else
-                                    C[(size_t)tok * p.ldc + row] = __float2half_rn(f + bv);
+                                    store1(C, (size_t)tok * p.ldc + row, f + bv, ok);
                             }
                         }
                     }
@@ -266,8 +296,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // split-K reduction: y[tok, n] = half(sum_s partial[s, tok, n] + bias[n])
 __global__ void __launch_bounds__(256)
-splitk_reduce_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, __half* __restrict__ y,
-                     int splits, size_t elems, int ldc) {
+splitk_reduce_kernel(const float* __restrict__ partial, const __half* __restrict__ bias, void* __restrict__ y,
+                     int splits, size_t elems, int ldc, int out_kind) {
     pdl_wait();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= elems) return;
@@ -282,9 +312,16 @@ splitk_reduce_kernel(const float* __restrict__ partial, const __half* __restrict
         acc.z += __half2float(bias[n + 2]); acc.w += __half2float(bias[n + 3]);
     }
     pdl_launch_dependents();
-    __half2* out = reinterpret_cast<__half2*>(y + i);
-    out[0] = __floats2half2_rn(acc.x, acc.y);
-    out[1] = __floats2half2_rn(acc.z, acc.w);
+    if (out_kind == 0) {
+        __half2* out = reinterpret_cast<__half2*>(reinterpret_cast<__half*>(y) + i);
+        out[0] = __floats2half2_rn(acc.x, acc.y);
+        out[1] = __floats2half2_rn(acc.z, acc.w);
+    } else if (out_kind == 1) {
+        __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(y) + i);
+        out[0] = __floats2bfloat162_rn(acc.x, acc.y);
+        out[1] = __floats2bfloat162_rn(acc.z, acc.w);
+    } else
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(y) + i) = acc;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -432,7 +469,7 @@ int gemm_tcgen05_f16(const void* x, const void* W, const void* bias, void* y, in
         if (rc != 0 || p.splits == 1) return rc;
         const size_t elems = (size_t)M * N;
         cudaError_t e = launch_k(splitk_reduce_kernel, dim3((unsigned)((elems / 4 + 255) / 256)), dim3(256), 0, s, true,
-                                 (const float*)p.partial, (const __half*)bias, (__half*)y, p.splits, elems, N);
+                                 (const float*)p.partial, (const __half*)bias, y, p.splits, elems, N, 0);
         count_launch();
         return (int)e;
     }
@@ -453,6 +490,75 @@ int gemm_tcgen05_f16(const void* x, const void* W, const void* bias, void* y, in
         case 128: return gemm_launch<128, false>(ma, mb, p, grid, s);
         default: return gemm_launch<256, false>(ma, mb, p, grid, s);
     }
+}
+
+// The same single-CTA kernel for the model families of b200_serve.h: operands fp16 or bfloat16, output fp16 / bfloat16 /
+// fp32 (out_kind as GemmParams), optionally with the GLU epilogue (W = [2 N, K], gate rows then up rows, N % 128 == 0).
+// Up to 256 token rows the weights stream through the M axis (swapped, split-K); above, tokens are the M axis.
+int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, bool glu, void* workspace,
+                    size_t workspace_bytes, cudaStream_t s) {
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    if (M < 1 || N < 8 || K < 8 || (K & 7) || !al(x) || !al(W) || !al(y)) return B200_EUNSUPPORTED;
+    const char* env = getenv("B200_NO_TCGEN05");
+    if (env && env[0] == '1') return B200_EUNSUPPORTED;
+    const int sms = sm_count();
+    GemmParams p{};
+    p.C = y; p.bias = nullptr; p.K = K; p.ldc = N; p.tokens = M;
+    p.k_blocks = (K + kBK - 1) / kBK;
+    p.in_bf16 = in_bf16; p.out_kind = out_kind;
+    CUtensorMap ma, mb;
+    if (glu) {
+        if (N < 128 || (N & 127)) return B200_EUNSUPPORTED;
+        p.rows_a = M; p.rows_b = N;
+        p.m_tiles = (M + kBM - 1) / kBM; p.n_tiles = N / 128; p.splits = 1;
+        if (!make_tma_map_2d(&ma, x, M, K, kBM) || !make_tma_map_2d(&mb, W, 2ll * N, K, 128)) return B200_EUNSUPPORTED;
+        const int units = p.m_tiles * p.n_tiles;
+        return gemm_launch<256, false, true>(ma, mb, p, units < sms ? units : sms, s);
+    }
+    if (M <= 256) {
+        const int BN = M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+        p.rows_a = N; p.rows_b = M;
+        p.m_tiles = (N + kBM - 1) / kBM; p.n_tiles = 1;
+        p.splits = pick_splits(p.m_tiles, p.k_blocks, sms);
+        if (p.splits > 1) {
+            const size_t need = (size_t)p.splits * M * N * sizeof(float);
+            if (!workspace || workspace_bytes < need || (N & 3)) p.splits = 1;
+            else p.partial = reinterpret_cast<float*>(workspace);
+        }
+        if (!make_tma_map_2d(&ma, W, N, K, kBM) || !make_tma_map_2d(&mb, x, M, K, BN)) return B200_EUNSUPPORTED;
+        const int units = p.m_tiles * p.splits;
+        const int grid = units < sms ? units : sms;
+        int rc;
+        switch (BN) {
+            case 32: rc = gemm_launch<32, true>(ma, mb, p, grid, s); break;
+            case 64: rc = gemm_launch<64, true>(ma, mb, p, grid, s); break;
+            case 128: rc = gemm_launch<128, true>(ma, mb, p, grid, s); break;
+            default: rc = gemm_launch<256, true>(ma, mb, p, grid, s); break;
+        }
+        if (rc != 0 || p.splits == 1) return rc;
+        const size_t elems = (size_t)M * N;
+        cudaError_t e = launch_k(splitk_reduce_kernel, dim3((unsigned)((elems / 4 + 255) / 256)), dim3(256), 0, s, true,
+                                 (const float*)p.partial, (const __half*)nullptr, y, p.splits, elems, N, out_kind);
+        count_launch();
+        return (int)e;
+    }
+    const int BN = N >= 256 ? 256 : N >= 128 ? 128 : N >= 64 ? 64 : 32;
+    p.rows_a = M; p.rows_b = N;
+    p.m_tiles = (M + kBM - 1) / kBM; p.n_tiles = (N + BN - 1) / BN; p.splits = 1;
+    if (!make_tma_map_2d(&ma, x, M, K, kBM) || !make_tma_map_2d(&mb, W, N, K, BN)) return B200_EUNSUPPORTED;
+    const int units = p.m_tiles * p.n_tiles;
+    const int grid = units < sms ? units : sms;
+    switch (BN) {
+        case 32: return gemm_launch<32, false>(ma, mb, p, grid, s);
+        case 64: return gemm_launch<64, false>(ma, mb, p, grid, s);
+        case 128: return gemm_launch<128, false>(ma, mb, p, grid, s);
+        default: return gemm_launch<256, false>(ma, mb, p, grid, s);
+    }
+}
+size_t gemm_tcgen05_ex_workspace_bytes(int M, int N, int K) {
+    if (M > 256) return 0;
+    const int splits = pick_splits((N + kBM - 1) / kBM, (K + kBK - 1) / kBK, sm_count());
+    return splits > 1 ? (size_t)splits * M * N * sizeof(float) : 0;
 }
 
 // out[M, inter] = silu(x W_gate^T) * (x W_up^T), W = [2*inter, K] (gate rows, then up rows): the gate_up GEMM of

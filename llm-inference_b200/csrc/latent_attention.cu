@@ -10,8 +10,9 @@
 //   latent_store_kernel        RMS norm (eps inside the root) of the down-projected row, times weight -> its page slot
 //   latent_attn_kernel         one CTA per (token, head): the warps walk the visible rows round-robin, each row read
 //                              coalesced by one warp; per-warp online softmax, merged with the sink at the end
-//   latent_attn_tile_kernel    bf16 tensor-core form (mma.sync): one CTA per 16 consecutive tokens x 4 heads of an entry;
-//                              rows staged in shared memory once per CTA and used for both the score and the weighted sum
+//   latent_attn_tile_kernel    bf16 tensor-core form (mma.sync): one CTA per 32 (token, head) rows; a tile of 64 cached
+//                              rows is staged in shared memory once and is the operand of both the scores and the
+//                              weighted sum (prompt portions and decoded tokens alike; the default for bf16 caches)
 #include "b200_serve.h"
 #include "common.cuh"
 #include "launch_count.h"
@@ -111,6 +112,216 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restric
         dst[r] = (so[r] * f[0] + so[rank + r] * f[1] + so[2 * rank + r] * f[2] + so[3 * rank + r] * f[3]) * inv;
 }
 
+
+// ---- bf16 tensor-core form ---------------------------------------------------------------------------------------
+// One CTA = 32 rows of (token, head) pairs: TQ consecutive tokens of the packed batch x HG heads (all heads share the
+// cached rows, so a row tile staged once serves HG heads). 8 warps. Per tile of 64 cached rows:
+//   S = Q C^T   : warp w computes the 8 keys [8w, 8w+8) for all 32 rows (k over the padded rank), scores to smem
+//   softmax     : warp w owns rows [4w, 4w+4): mask, running max / sum (fp32), P as bf16 to smem, rescale factors
+//   O += P C    : warp w owns output columns [64w', ...) of all 32 rows; the SAME smem tile is the B operand, read
+//                 transposed with ldmatrix.trans
+// The sink enters as the initial state (m = sink, l = 1, O = 0): a virtual row with a zero value.
+// Tokens of different sequences inside one CTA (entry borders, decode batches) are walked segment by segment.
+constexpr int kTileRows = 32, kTileKeys = 64, kTileWarps = 8;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int NT>   // n8 column tiles of the output per warp: padded rank <= 64 * NT
+__global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __restrict__ qa, float* __restrict__ out,
+                                                               const __nv_bfloat16* __restrict__ pool, const int* __restrict__ pages,
+                                                               int max_pages, int page_rows, const int* __restrict__ slot,
+                                                               const int* __restrict__ pos, const float* __restrict__ sink, float scale,
+                                                               int n_tokens, int heads, int rank, int HG, int TQ) {
+    using bf = __nv_bfloat16;
+    extern __shared__ __align__(16) unsigned char smraw[];
+    const int rpad = (rank + 15) & ~15, RS = rpad + 8;           // smem row stride in elements (16-byte multiple)
+    bf* Qs = reinterpret_cast<bf*>(smraw);                        // [32][RS]
+    bf* Ks = Qs + kTileRows * RS;                                 // [64][RS]
+    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [32][68]
+    bf* Ps = reinterpret_cast<bf*>(Ss + kTileRows * 68);          // [32][72]
+    float* alpha_s = reinterpret_cast<float*>(Ps + kTileRows * 72);   // [32]
+    float* linv_s = alpha_s + kTileRows;                          // [32]
+    int* row_pos = reinterpret_cast<int*>(linv_s + kTileRows);    // [32]: position of the row's token, -1 = inactive
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gid = lane / 4, tig = lane % 4;
+    const int t0 = blockIdx.x * TQ, h0 = blockIdx.y * HG;
+    const int ntok = min(TQ, n_tokens - t0);
+    const int n8 = rpad / 8;                                      // n8 tiles of the output
+    const int ntw = (n8 + kTileWarps - 1) / kTileWarps;           // per warp (<= NT)
+    const int tile0 = warp * ntw;
+
+    for (int first = 0; first < ntok;) {
+        const int sl = slot[t0 + first];
+        int cnt = 1;
+        while (first + cnt < ntok && slot[t0 + first + cnt] == sl) ++cnt;
+        const int n_keys = pos[t0 + first + cnt - 1] + 1;
+        const int* list = pages + (size_t)sl * max_pages;
+        __syncthreads();   // the previous segment's readers are done with the shared state
+        if (threadIdx.x < kTileRows) {
+            const int r = threadIdx.x, tl = r / HG, h = h0 + r % HG;
+            row_pos[r] = (tl >= first && tl < first + cnt && tl < TQ && h < heads) ? pos[t0 + tl] : -1;
+        }
+        for (int i = threadIdx.x; i < kTileRows * rpad; i += blockDim.x) {
+            const int r = i / rpad, c = i - r * rpad;
+            const int tl = r / HG, h = h0 + r % HG;
+            const bool on = tl >= first && tl < first + cnt && tl < TQ && h < heads && c < rank;
+            Qs[r * RS + c] = __float2bfloat16_rn(on ? qa[((size_t)(t0 + tl) * heads + h) * rank + c] : 0.f);
+        }
+        // running state of the rows this warp owns in the softmax phase (uniform over the lanes)
+        float m_run[4], l_run[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp * 4 + i, h = h0 + r % HG;
+            m_run[i] = h < heads ? sink[h] : 0.f;
+            l_run[i] = 1.f;
+        }
+        float o[2][NT][4];
+#pragma unroll
+        for (int a = 0; a < 2; ++a)
+#pragma unroll
+            for (int b = 0; b < NT; ++b)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[a][b][c] = 0.f;
+
+        for (int k0 = 0; k0 < n_keys; k0 += kTileKeys) {
+            __syncthreads();   // Ks / Ps / Ss of the previous tile are no longer read
+            if ((rank & 7) == 0) {
+                const int chunks = rpad / 8;
+                for (int i = threadIdx.x; i < kTileKeys * chunks; i += blockDim.x) {
+                    const int kr = i / chunks, ch = i - kr * chunks;
+                    const int j = k0 + kr;
+                    Pack16 v{};
+                    v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
+                    if (j < n_keys && ch * 8 < rank)
+                        v = ld16(pool + ((size_t)list[j / page_rows] * page_rows + j % page_rows) * rank + ch * 8);
+                    st16(Ks + kr * RS + ch * 8, v);
+                }
+            } else {
+                for (int i = threadIdx.x; i < kTileKeys * rpad; i += blockDim.x) {
+                    const int kr = i / rpad, c = i - kr * rpad;
+                    const int j = k0 + kr;
+                    bf v = __float2bfloat16_rn(0.f);
+                    if (j < n_keys && c < rank) v = pool[((size_t)list[j / page_rows] * page_rows + j % page_rows) * rank + c];
+                    Ks[kr * RS + c] = v;
+                }
+            }
+            __syncthreads();
+            {   // ---- scores of keys [8 warp, 8 warp + 8)
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                const bf* krow = Ks + (warp * 8 + gid) * RS + tig * 2;
+                for (int ks = 0; ks < rpad; ks += 16) {
+                    uint32_t a0[4], a1[4], b[2];
+                    ldsm_x4(a0, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks + (lane >> 4) * 8);
+                    ldsm_x4(a1, Qs + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks + (lane >> 4) * 8);
+                    b[0] = *reinterpret_cast<const uint32_t*>(krow + ks);
+                    b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 8);
+                    mma_bf16_16816(s[0], a0, b);
+                    mma_bf16_16816(s[1], a1, b);
+                }
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    float* d0 = Ss + (mt * 16 + gid) * 68 + warp * 8 + tig * 2;
+                    d0[0] = s[mt][0]; d0[1] = s[mt][1];
+                    d0[8 * 68] = s[mt][2]; d0[8 * 68 + 1] = s[mt][3];
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {   // ---- softmax of rows [4 warp, 4 warp + 4)
+                const int r = warp * 4 + i, rp = row_pos[r];
+                const int ka = k0 + lane, kb = k0 + lane + 32;
+                const float sa = ka <= rp ? Ss[r * 68 + lane] * scale : -INFINITY;
+                const float sb = kb <= rp ? Ss[r * 68 + lane + 32] * scale : -INFINITY;
+                float mx = fmaxf(sa, sb);
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+                const float mn = fmaxf(m_run[i], mx);           // finite: m starts at the sink
+                const float pa = ka <= rp ? expf(sa - mn) : 0.f, pb = kb <= rp ? expf(sb - mn) : 0.f;
+                float sum = pa + pb;
+#pragma unroll
+                for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
+                const float al = expf(m_run[i] - mn);
+                l_run[i] = l_run[i] * al + sum;
+                m_run[i] = mn;
+                Ps[r * 72 + lane] = __float2bfloat16_rn(pa);
+                Ps[r * 72 + lane + 32] = __float2bfloat16_rn(pb);
+                if (lane == 0) alpha_s[r] = al;
+            }
+            __syncthreads();
+            {   // ---- O = O * alpha + P C for this warp's output columns
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt) {
+                    const float a0 = alpha_s[mt * 16 + gid], a1 = alpha_s[mt * 16 + gid + 8];
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) { o[mt][nt][0] *= a0; o[mt][nt][1] *= a0; o[mt][nt][2] *= a1; o[mt][nt][3] *= a1; }
+                }
+#pragma unroll
+                for (int kk = 0; kk < kTileKeys; kk += 16) {
+                    uint32_t p0[4], p1[4];
+                    ldsm_x4(p0, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
+                    ldsm_x4(p1, Ps + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        const int tile = tile0 + nt;
+                        if (nt < ntw && tile < n8) {
+                            uint32_t b[2];
+                            ldsm_x2_trans(b, Ks + (kk + (lane & 15)) * RS + tile * 8);
+                            mma_bf16_16816(o[0][nt], p0, b);
+                            mma_bf16_16816(o[1][nt], p1, b);
+                        }
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) linv_s[warp * 4 + i] = 1.0f / l_run[i];
+        }
+        __syncthreads();
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int r = mt * 16 + gid + half * 8;
+                if (row_pos[r] < 0) continue;
+                const int tl = r / HG, h = h0 + r % HG;
+                float* dst = out + ((size_t)(t0 + tl) * heads + h) * rank;
+                const float inv = linv_s[r];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int tile = tile0 + nt;
+                    if (nt < ntw && tile < n8) {
+                        const int c = tile * 8 + tig * 2;
+                        if (c < rank) dst[c] = o[mt][nt][half * 2] * inv;
+                        if (c + 1 < rank) dst[c + 1] = o[mt][nt][half * 2 + 1] * inv;
+                    }
+                }
+            }
+        first += cnt;
+    }
+}
+
+static bool tile_attention_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("B200_LATENT_ATTN_SIMT");   // 1: the per-(token, head) kernel for bfloat16 caches too
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -142,6 +353,26 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = ((size_t)5 * rank + 8) * sizeof(float);
     dim3 grid(n_tokens, heads);
+    if (dtype == B200_BF16 && tile_attention_enabled()) {
+        // tensor-core form: 32 rows of (token, head) per CTA
+        const int HG = heads < kTileRows ? heads : kTileRows, TQ = kTileRows / HG;
+        const int rpad = (rank + 15) & ~15, RS = rpad + 8;
+        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + kTileRows * 68 * 4 + kTileRows * 72 * 2 + 3 * kTileRows * 4;
+        const int ntw = (rpad / 8 + kTileWarps - 1) / kTileWarps;
+        dim3 tg((n_tokens + TQ - 1) / TQ, (heads + HG - 1) / HG);
+        auto go = [&](auto kern) -> int {
+            static unsigned long long done = 0;
+            if (tsm > 48 * 1024 && ensure_max_dynamic_smem((const void*)kern, 200 * 1024, done) != cudaSuccess) return B200_EUNSUPPORTED;
+            kern<<<tg, 256, tsm, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens,
+                                      heads, rank, HG, TQ);
+            count_launch();
+            return (int)cudaGetLastError();
+        };
+        if (ntw <= 1) return go(latent_attn_tile_kernel<1>);
+        if (ntw <= 2) return go(latent_attn_tile_kernel<2>);
+        if (ntw <= 4) return go(latent_attn_tile_kernel<4>);
+        return go(latent_attn_tile_kernel<8>);
+    }
     if (dtype == B200_BF16)
         latent_attn_kernel<__nv_bfloat16><<<grid, 128, smem, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows,
                                                                  slot, pos, sink, scale, heads, rank);

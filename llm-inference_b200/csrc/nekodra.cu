@@ -51,6 +51,7 @@ public:
         if (stream_) cudaStreamSynchronize(stream_);
         for (void* p : owned_) cudaFree(p);
         cudaFree(scratch_);
+        cudaFree(ws_);
         cudaFree(capture_);
         if (logits_host_) cudaFreeHost(logits_host_);
         if (stream_) cudaStreamDestroy(stream_);
@@ -105,6 +106,8 @@ private:
     cudaStream_t stream_ = nullptr;
     // scratch, grown to the largest step seen
     char* scratch_ = nullptr;
+    void* ws_ = nullptr;          // split-K partials of the weight-streaming GEMM
+    size_t ws_bytes_ = 0;
     int cap_T_ = 0, cap_W_ = 0;
     float *x_ = nullptr, *proj_ = nullptr, *qa_ = nullptr, *oa_ = nullptr, *mix_ = nullptr, *eo_ = nullptr, *sh_ = nullptr,
           *weight_ = nullptr, *logits_ = nullptr;
@@ -354,6 +357,17 @@ int Nekodra::ensure_scratch(int T, int W) {
 
 int Nekodra::gemm(const void* A, int a_dt, long long lda, const void* W, long long ldw, void* C, int c_dt, long long ldc, int M,
                   int N, int K, int epi, const float* aux, long long ld_aux) {
+    if (lda == K && ldw == K && ldc == N && !aux && a_dt == dtype_) {   // contiguous: the tcgen05 GEMM when it fits
+        const size_t need = b200_linear_ex_workspace_bytes(M, N, K);
+        if (need > ws_bytes_) {
+            cudaStreamSynchronize(stream_);
+            cudaFree(ws_);
+            ws_ = nullptr;
+            ws_bytes_ = 0;
+            if (cudaMalloc(&ws_, need) == cudaSuccess) ws_bytes_ = need;   // without it the call runs with a single split
+        }
+        return b200_linear_ex(A, W, C, M, N, K, a_dt, c_dt, epi, ws_, ws_bytes_, stream_);
+    }
     b200_gemm_grouped_args g{};
     g.A = A; g.W = W; g.C = C; g.aux = aux;
     g.lda = lda; g.ldw = ldw; g.ldc = ldc; g.ld_aux = ld_aux;

@@ -31,6 +31,8 @@ SERVE_PROTOTYPES = {
     "b200_embed_positions": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200_layernorm_pair": (_i, [_vp, _vp, _i, _i, _f, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "b200_gemm_grouped": (_i, [C.POINTER(GemmGroupedArgs), _vp]),
+    "b200_linear_ex_workspace_bytes": (_sz, [_i, _i, _i]),
+    "b200_linear_ex": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "b200_latent_store": (_i, [_vp, _ll, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
     "b200_latent_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp]),
     "b200_moe_route": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
@@ -101,12 +103,15 @@ class Model:
         self.pages_total = L.b200_model_pages_total(self._h)
 
     def close(self):
-        if self._h:
+        if getattr(self, "_h", None):
             lib().b200_model_close(self._h)
             self._h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:   # interpreter shutdown: the module globals may be gone already
+            pass
 
     @property
     def pages_free(self):

@@ -220,7 +220,7 @@ def test_latent_attention_with_sink_over_pages(S, code, rank):
         c = seqs[slot[t]][:pos[t] + 1]
         for h in range(H):
             want = O.sink_attention(qa[t, h][None], c, c, scale, sink[h])[0]      # keys = values = the cached rows
-            assert rel(got[t, h], want) < 1e-4, (t, h)
+            assert rel(got[t, h], want) < (1e-4 if code == S.F32 else 2e-2), (t, h)   # bf16: the query and the weights are rounded for the tensor cores
 
 
 def test_latent_attention_far_key_stands_out(S):
@@ -306,3 +306,23 @@ def test_router_dispatch_combine(S, n_out, n_exp, top):
             d = int(destc[t, k])
             want[t] += wc[t, k] * (eo[d] if d >= 0 else h[t])
     assert rel(xd.cpu(), want) < 1e-5
+
+
+@pytest.mark.parametrize("M", [1, 8, 200, 257, 700])
+@pytest.mark.parametrize("N,K,glu", [(136, 64, False), (512, 192, False), (1000, 520, False), (128, 64, True), (384, 200, True)])
+@pytest.mark.parametrize("out", ["f32", "bf16"])
+def test_linear_ex_bf16_on_the_tcgen05_gemm(S, M, N, K, glu, out):
+    """contiguous bf16 products: weight-streaming (swapped, split-K) up to 256 rows, token-major above, GLU epilogue,
+    fp32 and bf16 outputs, ragged M / N / K tails"""
+    oc = S.BF16 if out == "bf16" else S.F32
+    g = torch.Generator().manual_seed(M + N)
+    x = dev(torch.randn(M, K, generator=g), torch.bfloat16)
+    W = dev(torch.randn((2 if glu else 1) * N, K, generator=g) / math.sqrt(K), torch.bfloat16)
+    y = torch.zeros(M, N, dtype=tdt(S, oc), device="cuda")
+    nbytes = S.lib().b200_linear_ex_workspace_bytes(M, N, K)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    sync_ok(S.lib().b200_linear_ex(x.data_ptr(), W.data_ptr(), y.data_ptr(), M, N, K, S.BF16, oc, S.GG_GLU if glu else S.GG_NONE,
+                                   ws.data_ptr(), nbytes, None))
+    xc, wc = x.float().cpu().double(), W.float().cpu().double()
+    want = (O.silu(xc @ wc[:N].T) * (xc @ wc[N:].T)) if glu else xc @ wc.T
+    assert rel(y.float().cpu(), want) < (1e-2 if oc == S.BF16 else 2e-5)
