@@ -15,6 +15,7 @@
 #include "common.cuh"
 #include "decode_step.h"
 #include "launch_count.h"
+#include "page_pool.h"
 
 namespace b200 {
 
@@ -69,12 +70,11 @@ struct b200_engine {
     // the device only ever reads the lists.
     bool kv_paged = false;
     int n_pages = 0, max_pages = 0;        // pool size; list length = ceil(max_seq / 128)
-    int* page_table = nullptr;             // device [batch, max_pages]
-    int* page_table_host = nullptr;        // pinned mirror (entries are only appended while a sequence lives)
+    b200::PagePool pool;                   // the allocator shared with the model families of b200_serve.h (page_pool.h)
+    int* page_table = nullptr;             // = pool.device(): device [batch, max_pages]
+    int* page_table_host = nullptr;        // = pool.host(): pinned mirror (+ batch ints of staging behind the lists)
     int* page_rows_dev = nullptr;          // device [batch]: rows per sequence, for gather (tests)
-    std::vector<int> free_pages, seq_pages;
     std::vector<char> seq_released;        // retired sequences whose pages went back (b200_engine_release_finished)
-    bool pages_dirty = false;              // the host lists hold entries the device copy does not have yet
     char* act_arena = nullptr;
     void *hidden, *residual, *qkv, *attn, *act, *gate_up, *logits, *partial;
     int *ids_cur, *ids_next, *step_dev;
@@ -553,16 +553,12 @@ extern "C" b200_engine* b200_engine_create_paged(const b200_model_config* c, int
         e->n_pages = n_pages > 0 ? n_pages : batch * e->max_pages;
         e->layer_kv_rows = (size_t)e->n_pages * e->hk * B200_KV_PAGE_ROWS;
         e->layer_kv_elems = e->layer_kv_rows * e->d;
-        const size_t tb = (size_t)batch * e->max_pages * sizeof(int);
-        if ((err = cudaMalloc(&e->page_table, tb + (size_t)batch * sizeof(int))) != cudaSuccess) return fail_free("cudaMalloc(page lists)", err);
-        cudaMemset(e->page_table, 0, tb + (size_t)batch * sizeof(int));
-        e->page_rows_dev = e->page_table + (size_t)batch * e->max_pages;
-        if ((err = cudaMallocHost(&e->page_table_host, tb + (size_t)batch * sizeof(int))) != cudaSuccess) return fail_free("cudaMallocHost(page lists)", err);
-        memset(e->page_table_host, 0, tb + (size_t)batch * sizeof(int));
-        e->seq_pages.assign(batch, 0);
+        if ((err = e->pool.init(e->n_pages, B200_KV_PAGE_ROWS, batch, e->max_pages, batch)) != cudaSuccess) return fail_free("page lists", err);
+        e->page_table = e->pool.device();
+        e->page_table_host = e->pool.host();
+        if ((err = cudaMalloc(&e->page_rows_dev, (size_t)batch * sizeof(int))) != cudaSuccess) return fail_free("cudaMalloc(page rows)", err);
+        cudaMemset(e->page_rows_dev, 0, (size_t)batch * sizeof(int));
         e->seq_released.assign(batch, 0);
-        e->free_pages.resize(e->n_pages);
-        for (int i = 0; i < e->n_pages; ++i) e->free_pages[i] = e->n_pages - 1 - i;   // page 0 is handed out first
     }
     e->kv_bytes_each = e->layer_kv_elems * c->num_layers * e->kv_esz;
     if (e->kv_fp8) {
@@ -647,8 +643,7 @@ extern "C" void b200_engine_destroy(b200_engine* e) {
     cudaFree(e->v_cache);
     cudaFree(e->k_scale);
     cudaFree(e->v_scale);
-    cudaFree(e->page_table);
-    if (e->page_table_host) cudaFreeHost(e->page_table_host);
+    cudaFree(e->page_rows_dev);   // the lists themselves belong to e->pool
     cudaFree(e->act_arena);
     delete e;
 }
@@ -671,7 +666,7 @@ extern "C" int b200_engine_get_step(const b200_engine* e) { return e->step; }
 extern "C" int b200_engine_kv_is_fp8(const b200_engine* e) { return e && e->kv_fp8 ? 1 : 0; }
 extern "C" int b200_engine_kv_is_paged(const b200_engine* e) { return e && e->kv_paged ? 1 : 0; }
 extern "C" int b200_engine_kv_pages_total(const b200_engine* e) { return e && e->kv_paged ? e->n_pages : 0; }
-extern "C" int b200_engine_kv_pages_free(const b200_engine* e) { return e && e->kv_paged ? (int)e->free_pages.size() : 0; }
+extern "C" int b200_engine_kv_pages_free(const b200_engine* e) { return e && e->kv_paged ? e->pool.free_count() : 0; }
 extern "C" const int* b200_engine_kv_page_table(const b200_engine* e) { return e && e->kv_paged ? e->page_table : nullptr; }
 /* paged cache only: K and V rows of every sequence gathered into dense [layers, B, hk, max_seq, d] DEVICE buffers */
 extern "C" int b200_engine_kv_gather(b200_engine* e, void* k_dst, void* v_dst) {
@@ -680,7 +675,7 @@ extern "C" int b200_engine_kv_gather(b200_engine* e, void* k_dst, void* v_dst) {
     int* rows_host = e->page_table_host + (size_t)e->batch * e->max_pages;
     int max_rows = 0;
     for (int b = 0; b < e->batch; ++b) {
-        rows_host[b] = std::min(e->seq_cached[b], e->seq_pages[b] * B200_KV_PAGE_ROWS);
+        rows_host[b] = std::min(e->seq_cached[b], e->pool.owned(b) * B200_KV_PAGE_ROWS);
         max_rows = std::max(max_rows, rows_host[b]);
     }
     CU(cudaMemcpyAsync(e->page_rows_dev, rows_host, (size_t)e->batch * sizeof(int), cudaMemcpyHostToDevice, e->stream));
@@ -764,30 +759,17 @@ extern "C" int b200_engine_set_p2p(b200_engine* e, b200_p2p* comm) {
 // Entries of a living sequence's list are only ever APPENDED, so a queued list upload that runs late and picks up newer
 // entries is harmless (kernels ahead of it never look past their own row count). Pages change owner only through
 // release_pages, which callers run behind a stream synchronisation.
-static void release_pages(b200_engine* e, int b) {
-    int* list = e->page_table_host + (size_t)b * e->max_pages;
-    for (int i = e->seq_pages[b] - 1; i >= 0; --i) e->free_pages.push_back(list[i]);
-    e->seq_pages[b] = 0;
-}
+static void release_pages(b200_engine* e, int b) { e->pool.release(b); }
 // make sure sequence b owns the pages of rows [0, rows); returns 1 if its list grew, 0 if not, < 0 on exhaustion
 static int ensure_pages(b200_engine* e, int b, int rows) {
-    const int need = (rows + B200_KV_PAGE_ROWS - 1) / B200_KV_PAGE_ROWS;
-    if (need > e->max_pages) return fail("paged KV: sequence longer than max_seq_len");
-    if (need <= e->seq_pages[b]) return 0;
-    if ((size_t)(need - e->seq_pages[b]) > e->free_pages.size())
+    const int r = e->pool.ensure(b, rows);
+    if (r == PagePool::kTooLong) return fail("paged KV: sequence longer than max_seq_len");
+    if (r == PagePool::kExhausted)
         return fail("paged KV: page pool exhausted (" + std::to_string(e->n_pages) + " pages of 128 rows)", B200_ENOMEM);
-    int* list = e->page_table_host + (size_t)b * e->max_pages;
-    while (e->seq_pages[b] < need) {
-        list[e->seq_pages[b]++] = e->free_pages.back();
-        e->free_pages.pop_back();
-    }
-    e->pages_dirty = true;
-    return 1;
+    return r;
 }
 static int upload_pages(b200_engine* e) {
-    CU(cudaMemcpyAsync(e->page_table, e->page_table_host, (size_t)e->batch * e->max_pages * sizeof(int),
-                       cudaMemcpyHostToDevice, e->stream));
-    e->pages_dirty = false;
+    CU(e->pool.upload(e->stream));
     return 0;
 }
 // pages for `rows_b[b]` rows of every sequence (rows_b[b] < 0: leave sequence b alone)
@@ -797,7 +779,7 @@ static int ensure_all_pages(b200_engine* e, const int* rows_b) {
         const int r = ensure_pages(e, b, rows_b[b]);
         if (r < 0) return r;   // lists that grew before the failure stay marked dirty and go up with the next call
     }
-    return e->pages_dirty ? upload_pages(e) : 0;
+    return e->pool.dirty() ? upload_pages(e) : 0;
 }
 
 static int set_step(b200_engine* e, int n) {
@@ -921,8 +903,8 @@ extern "C" int b200_engine_release_finished(b200_engine* e) {
     if (rc != 0) return rc > 0 ? -1000 - rc : rc;
     int released = 0;
     for (int b = 0; b < e->batch; ++b)
-        if (flags[b] && e->seq_pages[b] > 0) {
-            released += e->seq_pages[b];
+        if (flags[b] && e->pool.owned(b) > 0) {
+            released += e->pool.owned(b);
             release_pages(e, b);
             e->seq_released[b] = 1;
         }

@@ -127,14 +127,13 @@ int SequenceBatch::release(int slot) {
 // ------------------------------------------------------------------------------------------
 int generate_greedy(Model& m, int n_requests, const int* prompt_ids, const int* lens, int max_new, int eos_id, int chunk,
                     int* out_ids, int* n_generated, std::string& err) {
-    SequenceBatch& sq = m.sequences();
-    const int PR = sq.pool.page_rows();
+    const int PR = m.page_rows(), n_slots = m.n_slots(), n_pages = m.pages_total();
     struct Live { int req, slot, fed, made, last, pages; };
     std::vector<size_t> start(n_requests + 1, 0);
     for (int r = 0; r < n_requests; ++r) {
         if (lens[r] < 1) { err = "generate: empty prompt"; return B200_EINVAL; }
-        if (lens[r] + max_new - 1 > sq.max_positions) { err = "generate: prompt + new tokens exceed the model's positions"; return B200_EINVAL; }
-        if ((lens[r] + max_new - 1 + PR - 1) / PR > sq.pool.n_pages()) { err = "generate: a request does not fit the page pool"; return B200_ENOMEM; }
+        if (lens[r] + max_new - 1 > m.max_positions()) { err = "generate: prompt + new tokens exceed the model's positions"; return B200_EINVAL; }
+        if ((lens[r] + max_new - 1 + PR - 1) / PR > n_pages) { err = "generate: a request does not fit the page pool"; return B200_ENOMEM; }
         start[r + 1] = start[r] + lens[r];
     }
     for (size_t i = 0; i < (size_t)n_requests * max_new; ++i) out_ids[i] = eos_id;
@@ -142,10 +141,10 @@ int generate_greedy(Model& m, int n_requests, const int* prompt_ids, const int* 
     std::deque<int> waiting;
     for (int r = 0; r < n_requests; ++r) waiting.push_back(r);
     std::vector<Live> live;
-    std::vector<char> slot_used(sq.n_slots, 0);
-    for (int b = 0; b < sq.n_slots; ++b) slot_used[b] = sq.length[b] > 0;   // slots the caller holds stay untouched
+    std::vector<char> slot_used(n_slots, 0);
+    for (int b = 0; b < n_slots; ++b) slot_used[b] = m.slot_length(b) > 0;   // slots the caller holds stay untouched
     int reserved = 0;   // pages promised to the live requests over their whole life
-    for (int b = 0; b < sq.n_slots; ++b) reserved += sq.pool.owned(b);
+    for (int b = 0; b < n_slots; ++b) reserved += m.slot_page_count(b);
     int steps = 0;
     std::vector<StepEntry> entries;
     std::vector<int> want_last, ids, dec_tok;
@@ -155,9 +154,9 @@ int generate_greedy(Model& m, int n_requests, const int* prompt_ids, const int* 
             const int r = waiting.front();
             const int need = (lens[r] + max_new - 1 + PR - 1) / PR;
             int slot = -1;
-            for (int b = 0; b < sq.n_slots; ++b)
+            for (int b = 0; b < n_slots; ++b)
                 if (!slot_used[b]) { slot = b; break; }
-            if (slot < 0 || reserved + need > sq.pool.n_pages()) break;
+            if (slot < 0 || reserved + need > n_pages) break;
             slot_used[slot] = 1;
             reserved += need;
             live.push_back({r, slot, 0, 0, 0, need});
@@ -277,20 +276,17 @@ extern "C" const char* b200_model_family(const b200_model* m) { return m ? m->im
 extern "C" int b200_model_vocab(const b200_model* m) { return m ? m->impl->vocab() : 0; }
 extern "C" int b200_model_width(const b200_model* m) { return m ? m->impl->width() : 0; }
 extern "C" int b200_model_layer_count(const b200_model* m) { return m ? m->impl->layer_count() : 0; }
-extern "C" int b200_model_max_positions(const b200_model* m) { return m ? m->impl->sequences().max_positions : 0; }
-extern "C" int b200_model_page_rows(const b200_model* m) { return m ? m->impl->sequences().pool.page_rows() : 0; }
-extern "C" int b200_model_pages_total(const b200_model* m) { return m ? m->impl->sequences().pool.n_pages() : 0; }
-extern "C" int b200_model_pages_free(const b200_model* m) { return m ? m->impl->sequences().pool.free_count() : 0; }
+extern "C" int b200_model_max_positions(const b200_model* m) { return m ? m->impl->max_positions() : 0; }
+extern "C" int b200_model_page_rows(const b200_model* m) { return m ? m->impl->page_rows() : 0; }
+extern "C" int b200_model_pages_total(const b200_model* m) { return m ? m->impl->pages_total() : 0; }
+extern "C" int b200_model_pages_free(const b200_model* m) { return m ? m->impl->pages_free() : 0; }
 extern "C" int b200_model_slot_length(const b200_model* m, int slot) {
-    if (!m || slot < 0 || slot >= m->impl->sequences().n_slots) return B200_EINVAL;
-    return m->impl->sequences().length[slot];
+    if (!m || slot < 0 || slot >= m->impl->n_slots()) return B200_EINVAL;
+    return m->impl->slot_length(slot);
 }
 extern "C" int b200_model_slot_pages(const b200_model* m, int slot, int* out, int max_n) {
-    if (!m || !out || slot < 0 || slot >= m->impl->sequences().n_slots) return B200_EINVAL;
-    const PagePool& p = m->impl->sequences().pool;
-    const int n = std::min(max_n, p.owned(slot));
-    for (int i = 0; i < n; ++i) out[i] = p.list(slot)[i];
-    return n;
+    if (!m || !out || slot < 0 || slot >= m->impl->n_slots()) return B200_EINVAL;
+    return m->impl->slot_pages(slot, out, max_n);
 }
 
 extern "C" int b200_model_step(b200_model* m, int n_entries, const int* slots, const int* n_tokens, const int* tokens,
@@ -332,7 +328,7 @@ extern "C" int b200_model_generate(b200_model* m, int n_requests, const int* pro
 extern "C" b200_session* b200_session_create(b200_model* m) {
     if (!m) return nullptr;
     b200_session* s = new b200_session{m, {}, {}};
-    s->used.assign(m->impl->sequences().n_slots, 0);
+    s->used.assign(m->impl->n_slots(), 0);
     return s;
 }
 extern "C" void b200_session_destroy(b200_session* s) { delete s; }

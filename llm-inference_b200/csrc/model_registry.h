@@ -63,7 +63,15 @@ public:
     virtual int vocab() const = 0;
     virtual int width() const = 0;
     virtual int layer_count() const = 0;
-    virtual SequenceBatch& sequences() = 0;
+    // sequence slots and the page pool behind the cache
+    virtual int n_slots() const = 0;
+    virtual int max_positions() const = 0;
+    virtual int page_rows() const = 0;
+    virtual int pages_total() const = 0;
+    virtual int pages_free() const = 0;
+    virtual int slot_length(int slot) const = 0;
+    virtual int slot_page_count(int slot) const = 0;
+    virtual int slot_pages(int slot, int* out, int max_n) const = 0;
     // entries as ONE batch; logits_out host fp32 [sum n_want, vocab] and ids_out host [sum n_want] may be NULL
     virtual int step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) = 0;
     virtual int release(int slot) = 0;

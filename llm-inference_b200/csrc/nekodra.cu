@@ -16,6 +16,7 @@
 //   grouped down GEMM;   shared GLU GEMM -> down GEMM;   x += mixer + routed + shared (one kernel).
 #include <cuda_bf16.h>
 
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -60,7 +61,18 @@ public:
     int vocab() const override { return vocab_; }
     int width() const override { return D_; }
     int layer_count() const override { return (int)layers_.size(); }
-    SequenceBatch& sequences() override { return seq_; }
+    int n_slots() const override { return seq_.n_slots; }
+    int max_positions() const override { return seq_.max_positions; }
+    int page_rows() const override { return seq_.pool.page_rows(); }
+    int pages_total() const override { return seq_.pool.n_pages(); }
+    int pages_free() const override { return seq_.pool.free_count(); }
+    int slot_length(int slot) const override { return seq_.length[slot]; }
+    int slot_page_count(int slot) const override { return seq_.pool.owned(slot); }
+    int slot_pages(int slot, int* out, int max_n) const override {
+        const int n = std::min(max_n, seq_.pool.owned(slot));
+        for (int i = 0; i < n; ++i) out[i] = seq_.pool.list(slot)[i];
+        return n;
+    }
     int step_launches() const override { return launches_; }
 
     int load(const ModelDir& dir, const b200_model_options& opt, std::string& err);
