@@ -77,10 +77,15 @@ int b200_latent_store(const float* raw, long long ld_raw, const float* w, float 
  * pos[t]) and head h: s_j = scale * <qa[t,h,:], c_j> over the sequence's rows j <= pos[t]; p_j = exp(s_j - m) /
  * (sum_j exp(s_j - m) + exp(sink[h] - m)); out[t,h,:] = sum_j p_j c_j. qa, out fp32 [n_tokens, heads, rank] (qa is the
  * query already multiplied by the key up-projection; the caller applies the value up-projection to out). The sink
- * has no row and no value. Rows come from the page pool as in b200_latent_store. */
+ * has no row and no value. Rows come from the page pool as in b200_latent_store.
+ * Hints (0 / NULL = unknown): longest_entry = most consecutive tokens of one sequence in the batch (1: a decode batch,
+ * one token per CTA); longest_context = most rows any token sees; with a workspace the bfloat16 kernel then splits long
+ * contexts of small batches over several CTAs and merges the shares (and the sink) in a second launch. */
+size_t b200_latent_attention_workspace_bytes(int n_tokens, int heads, int rank);
 int b200_latent_attention(const float* qa, float* out, const void* pool, const int* pages, int max_pages, int page_rows,
                           const int* slot, const int* pos, const float* sink, float scale, int n_tokens, int heads,
-                          int rank, int dtype, void* stream);
+                          int rank, int dtype, int longest_entry, int longest_context, void* workspace,
+                          size_t workspace_bytes, void* stream);
 
 /* Router of a mixture of experts with identity experts: z = h W_r^T (fp32 accumulate; h of h_dtype, W_r fp32
  * [n_out, width]); s = softmax(z) over all n_out outputs; the `top` largest of s + correction are chosen; their weights

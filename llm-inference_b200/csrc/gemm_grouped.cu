@@ -140,7 +140,23 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <typename TA, typename TC, bool TRANS_B, bool GLU>
+// eight consecutive elements as bf16 in one 16-byte packet (fp32 sources are rounded on the way)
+template <typename T> __device__ __forceinline__ Pack16 load8_bf16(const T* p);
+template <> __device__ __forceinline__ Pack16 load8_bf16<__nv_bfloat16>(const __nv_bfloat16* p) { return ld16(p); }
+template <> __device__ __forceinline__ Pack16 load8_bf16<float>(const float* p) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    Pack16 v;
+    __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(a.x, a.y); v.w[0] = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(a.z, a.w); v.w[1] = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(b.x, b.y); v.w[2] = *reinterpret_cast<uint32_t*>(&h);
+    h = __floats2bfloat162_rn(b.z, b.w); v.w[3] = *reinterpret_cast<uint32_t*>(&h);
+    return v;
+}
+
+// VEC: every row of A and W starts on a 16-byte boundary (32 for fp32 A) and K % 8 == 0: 16-byte global loads, the next
+// k tile fetched into registers while the tensor cores work on the current one
+template <typename TA, typename TC, bool TRANS_B, bool GLU, bool VEC = false>
 __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
     using bf = __nv_bfloat16;
     __shared__ __align__(16) bf As[GBM][MBK + MPAD];
@@ -181,7 +197,34 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
         arow[threadIdx.x] = src;
     }
     __syncthreads();
+    // VEC: 64 rows x 32 k = 256 packets of 8 per operand tile, two per thread
+    Pack16 ra[2], rb[GLU ? 4 : 2];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int c = threadIdx.x + i * 128, r = c >> 2, gk = k0 + (c & 3) * 8;
+            const long long src = arow[r];
+            Pack16 z; z.w[0] = z.w[1] = z.w[2] = z.w[3] = 0u;
+            ra[i] = (src >= 0 && gk < K) ? load8_bf16<TA>(A + src * g.lda + gk) : z;
+            const int gn = n0 + r;
+            const bool ok = gn < N && gk < K;
+            rb[i] = ok ? ld16(W + (long long)gn * g.ldw + gk) : z;
+            if (GLU) rb[GLU ? 2 + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
+        }
+    };
+    if (VEC) fetch(0);
     for (int k0 = 0; k0 < K; k0 += MBK) {
+        if (VEC) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c = threadIdx.x + i * 128, r = c >> 2, kc = (c & 3) * 8;
+                st16(&As[r][kc], ra[i]);
+                st16(&Bs[0][r][kc], rb[i]);
+                if (GLU) st16(&Bs[GLU ? 1 : 0][r][kc], rb[GLU ? 2 + i : 0]);
+            }
+            __syncthreads();
+            if (k0 + MBK < K) fetch(k0 + MBK);
+        } else {
         for (int i = threadIdx.x; i < GBM * MBK; i += 128) {
             const int r = i / MBK, kk = i - r * MBK;
             const int gk = k0 + kk;
@@ -204,6 +247,7 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
             }
         }
         __syncthreads();
+        }
 #pragma unroll
         for (int ks = 0; ks < MBK; ks += 16) {
             uint32_t a[2][4];
@@ -259,12 +303,17 @@ static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) 
 }
 template <typename TA, typename TC>
 static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
+    auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
+    const bool vec = trans_b && g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
+                     al(g.A, sizeof(TA) * 8) && al(g.W, 16);
     if (g.epi == B200_GG_GLU) {
         if (!trans_b) return B200_EUNSUPPORTED;
-        gemm_grouped_mma_kernel<TA, TC, true, true><<<grid, 128, 0, s>>>(g);
-    } else if (trans_b)
-        gemm_grouped_mma_kernel<TA, TC, true, false><<<grid, 128, 0, s>>>(g);
-    else
+        if (vec) gemm_grouped_mma_kernel<TA, TC, true, true, true><<<grid, 128, 0, s>>>(g);
+        else gemm_grouped_mma_kernel<TA, TC, true, true><<<grid, 128, 0, s>>>(g);
+    } else if (trans_b) {
+        if (vec) gemm_grouped_mma_kernel<TA, TC, true, false, true><<<grid, 128, 0, s>>>(g);
+        else gemm_grouped_mma_kernel<TA, TC, true, false><<<grid, 128, 0, s>>>(g);
+    } else
         gemm_grouped_mma_kernel<TA, TC, false, false><<<grid, 128, 0, s>>>(g);
     return (int)cudaGetLastError();
 }

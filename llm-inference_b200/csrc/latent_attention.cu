@@ -13,6 +13,8 @@
 //   latent_attn_tile_kernel    bf16 tensor-core form (mma.sync): one CTA per 32 (token, head) rows; a tile of 64 cached
 //                              rows is staged in shared memory once and is the operand of both the scores and the
 //                              weighted sum (prompt portions and decoded tokens alike; the default for bf16 caches)
+#include <algorithm>
+
 #include "b200_serve.h"
 #include "common.cuh"
 #include "launch_count.h"
@@ -122,7 +124,7 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restric
 //                 transposed with ldmatrix.trans
 // The sink enters as the initial state (m = sink, l = 1, O = 0): a virtual row with a zero value.
 // Tokens of different sequences inside one CTA (entry borders, decode batches) are walked segment by segment.
-constexpr int kTileRows = 32, kTileKeys = 64, kTileWarps = 8;
+constexpr int kTileRows = 32, kTileKeys = 64, kTileWarps = 8, kMaxSplits = 16;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -143,7 +145,10 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
                                                                const __nv_bfloat16* __restrict__ pool, const int* __restrict__ pages,
                                                                int max_pages, int page_rows, const int* __restrict__ slot,
                                                                const int* __restrict__ pos, const float* __restrict__ sink, float scale,
-                                                               int n_tokens, int heads, int rank, int HG, int TQ) {
+                                                               int n_tokens, int heads, int rank, int HG, int TQ, int splits,
+                                                               float* __restrict__ part) {
+    // splits > 1 (blockIdx.z): this CTA walks one share of the key tiles and leaves (m, l, unnormalised O) per row in
+    // `part` [token, head, split, 2 + rank]; latent_attn_combine_kernel merges the shares and the sink
     using bf = __nv_bfloat16;
     extern __shared__ __align__(16) unsigned char smraw[];
     const int rpad = (rank + 15) & ~15, RS = rpad + 8;           // smem row stride in elements (16-byte multiple)
@@ -166,7 +171,9 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
         const int sl = slot[t0 + first];
         int cnt = 1;
         while (first + cnt < ntok && slot[t0 + first + cnt] == sl) ++cnt;
-        const int n_keys = pos[t0 + first + cnt - 1] + 1;
+        const int all_keys = pos[t0 + first + cnt - 1] + 1;
+        const int per = ((all_keys + kTileKeys - 1) / kTileKeys + splits - 1) / splits * kTileKeys;   // keys per share
+        const int key_lo = blockIdx.z * per, n_keys = min(all_keys, key_lo + per);
         const int* list = pages + (size_t)sl * max_pages;
         __syncthreads();   // the previous segment's readers are done with the shared state
         if (threadIdx.x < kTileRows) {
@@ -184,8 +191,8 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = warp * 4 + i, h = h0 + r % HG;
-            m_run[i] = h < heads ? sink[h] : 0.f;
-            l_run[i] = 1.f;
+            m_run[i] = splits > 1 ? -1e30f : (h < heads ? sink[h] : 0.f);   // shares: the sink joins in the combine
+            l_run[i] = splits > 1 ? 0.f : 1.f;
         }
         float o[2][NT][4];
 #pragma unroll
@@ -195,7 +202,7 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
 #pragma unroll
                 for (int c = 0; c < 4; ++c) o[a][b][c] = 0.f;
 
-        for (int k0 = 0; k0 < n_keys; k0 += kTileKeys) {
+        for (int k0 = key_lo; k0 < n_keys; k0 += kTileKeys) {
             __syncthreads();   // Ks / Ps / Ss of the previous tile are no longer read
             if ((rank & 7) == 0) {
                 const int chunks = rpad / 8;
@@ -287,7 +294,15 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
         }
         if (lane == 0) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) linv_s[warp * 4 + i] = 1.0f / l_run[i];
+            for (int i = 0; i < 4; ++i) {
+                const int r = warp * 4 + i;
+                linv_s[r] = splits > 1 ? 1.0f : 1.0f / l_run[i];
+                if (splits > 1 && row_pos[r] >= 0) {
+                    float* pr = part + (((size_t)(t0 + r / HG) * heads + h0 + r % HG) * splits + blockIdx.z) * (rank + 2);
+                    pr[0] = m_run[i];
+                    pr[1] = l_run[i];
+                }
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -297,7 +312,8 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
                 const int r = mt * 16 + gid + half * 8;
                 if (row_pos[r] < 0) continue;
                 const int tl = r / HG, h = h0 + r % HG;
-                float* dst = out + ((size_t)(t0 + tl) * heads + h) * rank;
+                float* dst = splits > 1 ? part + (((size_t)(t0 + tl) * heads + h) * splits + blockIdx.z) * (rank + 2) + 2
+                                        : out + ((size_t)(t0 + tl) * heads + h) * rank;
                 const float inv = linv_s[r];
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
@@ -310,6 +326,24 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
                 }
             }
         first += cnt;
+    }
+}
+
+// merges the shares of a split launch: grid (token, head)
+__global__ void __launch_bounds__(128) latent_attn_combine_kernel(const float* __restrict__ part, float* __restrict__ out,
+                                                                  const float* __restrict__ sink, int heads, int rank, int splits) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* p = part + ((size_t)t * heads + h) * splits * (rank + 2);
+    const float sk = sink[h];
+    float M = sk;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, p[(size_t)z * (rank + 2)]);
+    float den = expf(sk - M);
+    for (int z = 0; z < splits; ++z) den += p[(size_t)z * (rank + 2) + 1] * expf(p[(size_t)z * (rank + 2)] - M);
+    const float inv = 1.0f / den;
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float acc = 0.f;
+        for (int z = 0; z < splits; ++z) acc += p[(size_t)z * (rank + 2) + 2 + c] * expf(p[(size_t)z * (rank + 2)] - M);
+        out[((size_t)t * heads + h) * rank + c] = acc * inv;
     }
 }
 
@@ -344,9 +378,14 @@ extern "C" int b200_latent_store(const float* raw, long long ld_raw, const float
     return (int)cudaGetLastError();
 }
 
+extern "C" size_t b200_latent_attention_workspace_bytes(int n_tokens, int heads, int rank) {
+    return (size_t)n_tokens * heads * kMaxSplits * (rank + 2) * sizeof(float);
+}
+
 extern "C" int b200_latent_attention(const float* qa, float* out, const void* pool, const int* pages, int max_pages,
                                      int page_rows, const int* slot, const int* pos, const float* sink, float scale,
-                                     int n_tokens, int heads, int rank, int dtype, void* stream) {
+                                     int n_tokens, int heads, int rank, int dtype, int longest_entry, int longest_context,
+                                     void* workspace, size_t workspace_bytes, void* stream) {
     if (!qa || !out || !pool || !pages || !slot || !pos || !sink || n_tokens < 0 || heads < 1 || rank < 1) return B200_EINVAL;
     if (rank > 32 * kMaxRankPerLane || heads > 65535) return B200_EUNSUPPORTED;
     if (n_tokens == 0) return B200_OK;
@@ -355,17 +394,32 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
     dim3 grid(n_tokens, heads);
     if (dtype == B200_BF16 && tile_attention_enabled()) {
         // tensor-core form: 32 rows of (token, head) per CTA
-        const int HG = heads < kTileRows ? heads : kTileRows, TQ = kTileRows / HG;
+        // every entry a single token (a decode batch): one token per CTA, its heads the only rows
+        const int HG = heads < kTileRows ? heads : kTileRows, TQ = longest_entry == 1 ? 1 : kTileRows / HG;
         const int rpad = (rank + 15) & ~15, RS = rpad + 8;
         const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + kTileRows * 68 * 4 + kTileRows * 72 * 2 + 3 * kTileRows * 4;
         const int ntw = (rpad / 8 + kTileWarps - 1) / kTileWarps;
         dim3 tg((n_tokens + TQ - 1) / TQ, (heads + HG - 1) / HG);
+        // few CTAs over long contexts (decoding): shares of the key tiles on blockIdx.z, merged by the combine kernel
+        int splits = 1;
+        if (longest_context > 0 && workspace) {
+            const int tiles = (longest_context + kTileKeys - 1) / kTileKeys;
+            const int want = (2 * sm_count()) / (int)(tg.x * tg.y);
+            splits = std::max(1, std::min({want, tiles / 2, kMaxSplits}));
+            if (workspace_bytes < (size_t)n_tokens * heads * splits * (rank + 2) * sizeof(float)) splits = 1;
+        }
+        tg.z = splits;
+        float* part = reinterpret_cast<float*>(workspace);
         auto go = [&](auto kern) -> int {
             static unsigned long long done = 0;
             if (tsm > 48 * 1024 && ensure_max_dynamic_smem((const void*)kern, 200 * 1024, done) != cudaSuccess) return B200_EUNSUPPORTED;
             kern<<<tg, 256, tsm, s>>>(qa, out, (const __nv_bfloat16*)pool, pages, max_pages, page_rows, slot, pos, sink, scale, n_tokens,
-                                      heads, rank, HG, TQ);
+                                      heads, rank, HG, TQ, splits, part);
             count_launch();
+            if (splits > 1) {
+                latent_attn_combine_kernel<<<dim3(n_tokens, heads), 128, 0, s>>>(part, out, sink, heads, rank, splits);
+                count_launch();
+            }
             return (int)cudaGetLastError();
         };
         if (ntw <= 1) return go(latent_attn_tile_kernel<1>);

@@ -53,6 +53,7 @@ public:
         for (void* p : owned_) cudaFree(p);
         cudaFree(scratch_);
         cudaFree(ws_);
+        cudaFree(attn_ws_);
         cudaFree(capture_);
         if (logits_host_) cudaFreeHost(logits_host_);
         if (stream_) cudaStreamDestroy(stream_);
@@ -120,6 +121,8 @@ private:
     char* scratch_ = nullptr;
     void* ws_ = nullptr;          // split-K partials of the weight-streaming GEMM
     size_t ws_bytes_ = 0;
+    void* attn_ws_ = nullptr;     // shares of split-context attention (decode batches)
+    size_t attn_ws_bytes_ = 0;
     int cap_T_ = 0, cap_W_ = 0;
     float *x_ = nullptr, *proj_ = nullptr, *qa_ = nullptr, *oa_ = nullptr, *mix_ = nullptr, *eo_ = nullptr, *sh_ = nullptr,
           *weight_ = nullptr, *logits_ = nullptr;
@@ -394,6 +397,22 @@ int Nekodra::step(const std::vector<StepEntry>& entries, float* logits_out, int*
     NK_TRY(seq_.begin_step(entries, stream_, err));
     const int T = seq_.n_tokens, W = seq_.n_want, D = D_, dt = dtype_;
     if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
+    int longest_entry = 0, longest_context = 0;
+    for (const StepEntry& en : entries) {
+        longest_entry = std::max(longest_entry, en.n_tokens);
+        longest_context = std::max(longest_context, seq_.length[en.slot]);
+    }
+    if (longest_entry == 1) {   // a decode batch: room for the shares of split contexts
+        size_t need = 0;
+        for (const NkLayer& L : layers_) need = std::max(need, b200_latent_attention_workspace_bytes(T, L.heads, L.rank));
+        if (need > attn_ws_bytes_) {
+            cudaStreamSynchronize(stream_);
+            cudaFree(attn_ws_);
+            attn_ws_ = nullptr;
+            attn_ws_bytes_ = 0;
+            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
+        }
+    }
     const int* pages = seq_.pool.device();
     const int max_pages = seq_.pool.max_pages();
     if (capture_on_) {
@@ -433,7 +452,7 @@ int Nekodra::step(const std::vector<StepEntry>& entries, float* logits_out, int*
             NK_OP(b200_gemm_grouped(&g, stream_));
         }
         NK_OP(b200_latent_attention(qa_, oa_, pools_[L.cache], pages, max_pages, kPageRows, seq_.d_slot(), seq_.d_pos(), L.sink,
-                                    L.scale, T, H, R, dt, stream_));
+                                    L.scale, T, H, R, dt, longest_entry, longest_context, attn_ws_, attn_ws_bytes_, stream_));
         {   // att[t, h, :] = (W_uv,h oa[t, h, :]) * sigmoid(gate[t, h, :])
             b200_gemm_grouped_args g{};
             g.A = oa_; g.lda = (long long)H * R; g.stride_a = R;

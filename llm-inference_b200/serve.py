@@ -34,7 +34,8 @@ SERVE_PROTOTYPES = {
     "b200_linear_ex_workspace_bytes": (_sz, [_i, _i, _i]),
     "b200_linear_ex": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "b200_latent_store": (_i, [_vp, _ll, _vp, _f, _vp, _vp, _i, _i, _vp, _vp, _i, _i, _i, _vp]),
-    "b200_latent_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _f, _i, _i, _i, _i, _vp]),
+    "b200_latent_attention_workspace_bytes": (_sz, [_i, _i, _i]),
+    "b200_latent_attention": (_i, [_vp, _vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _f, _i, _i, _i, _i, _i, _i, _vp, _sz, _vp]),
     "b200_moe_route": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "b200_moe_dispatch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_residual_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),

@@ -214,7 +214,7 @@ def test_latent_attention_with_sink_over_pages(S, code, rank):
     scale = 0.7
     sync_ok(S.lib().b200_latent_attention(dev(qa).data_ptr(), out.data_ptr(), dev(pool).data_ptr(), dev(table).data_ptr(), max_pages, PR,
                                           dev(torch.tensor(slot, dtype=torch.int32)).data_ptr(), dev(torch.tensor(pos, dtype=torch.int32)).data_ptr(),
-                                          dev(sink).data_ptr(), scale, T, H, rank, code, None))
+                                          dev(sink).data_ptr(), scale, T, H, rank, code, 0, 0, None, 0, None))
     got = out.cpu()
     for t in range(T):
         c = seqs[slot[t]][:pos[t] + 1]
@@ -232,10 +232,35 @@ def test_latent_attention_far_key_stands_out(S):
     out = torch.zeros(1, 1, R, device="cuda")
     sync_ok(S.lib().b200_latent_attention(dev(qa).data_ptr(), out.data_ptr(), dev(pool).data_ptr(), dev(table).data_ptr(), max_pages, PR,
                                           dev(torch.tensor([0], dtype=torch.int32)).data_ptr(), dev(torch.tensor([699], dtype=torch.int32)).data_ptr(),
-                                          dev(torch.tensor([0.0])).data_ptr(), 1.0, 1, 1, R, S.F32, None))
+                                          dev(torch.tensor([0.0])).data_ptr(), 1.0, 1, 1, R, S.F32, 0, 0, None, 0, None))
     want = O.sink_attention(qa[0, 0][None], seqs[0], seqs[0], 1.0, torch.tensor(0.0))[0]
     assert rel(out.cpu()[0, 0], want) < 1e-4
     assert rel(out.cpu()[0, 0], seqs[0][3]) < 1e-2   # and it IS row 3, to within the softmax tail
+
+
+@pytest.mark.parametrize("heads", [1, 5, 16])
+def test_latent_attention_decode_batch_with_split_contexts(S, heads):
+    """one token per sequence over contexts of very different lengths: the bf16 kernel splits the rows over several CTAs
+    and merges the shares with the sink afterwards; a context shorter than one share, and one of a single row"""
+    PR, R = 64, 72
+    lengths = [1, 50, 700, 1300]
+    seqs, pool, table, max_pages = paged(S, lengths, R, PR, S.BF16, seed=heads)
+    g = torch.Generator().manual_seed(3)
+    T = len(lengths)
+    qa = torch.randn(T, heads, R, generator=g) * (3.0 / math.sqrt(R))
+    sink = torch.randn(heads, generator=g) * 2
+    out = torch.zeros(T, heads, R, device="cuda")
+    nbytes = S.lib().b200_latent_attention_workspace_bytes(T, heads, R)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+    sync_ok(S.lib().b200_latent_attention(dev(qa).data_ptr(), out.data_ptr(), dev(pool).data_ptr(), dev(table).data_ptr(), max_pages, PR,
+                                          dev(torch.arange(T, dtype=torch.int32)).data_ptr(),
+                                          dev(torch.tensor([n - 1 for n in lengths], dtype=torch.int32)).data_ptr(),
+                                          dev(sink).data_ptr(), 0.6, T, heads, R, S.BF16, 1, max(lengths), ws.data_ptr(), nbytes, None))
+    got = out.cpu()
+    for t in range(T):
+        for h in range(heads):
+            want = O.sink_attention(qa[t, h][None], seqs[t], seqs[t], 0.6, sink[h])[0]
+            assert rel(got[t, h], want) < 2e-2, (t, h)
 
 
 @pytest.mark.parametrize("code", ["f32", "bf16"])
