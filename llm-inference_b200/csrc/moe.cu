@@ -12,14 +12,26 @@ template <typename T>
 __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ corr, int width, int n_out, int top,
                                                         float scale, int* __restrict__ chosen, float* __restrict__ weight) {
-    extern __shared__ float z[];   // z[n_out] | pick[n_out]
+    extern __shared__ float z[];   // z[n_out] | pick[n_out] | x[width]
     float* pick = z + n_out;
+    float* xs = pick + n_out;
     const int t = blockIdx.x, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const T* x = h + (size_t)t * width;
+    // the token's input once in shared memory as fp32, then four independent partial sums per lane
+    for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = DT<T>::to_f(x[i]);
+    __syncthreads();
     for (int o = warp; o < n_out; o += 4) {
         const float* w = wr + (size_t)o * width;
-        float d = 0.f;
-        for (int i = lane; i < width; i += 32) d = fmaf(DT<T>::to_f(x[i]), w[i], d);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        int i = lane;
+        for (; i + 96 < width; i += 128) {
+            d0 = fmaf(xs[i], w[i], d0);
+            d1 = fmaf(xs[i + 32], w[i + 32], d1);
+            d2 = fmaf(xs[i + 64], w[i + 64], d2);
+            d3 = fmaf(xs[i + 96], w[i + 96], d3);
+        }
+        for (; i < width; i += 32) d0 = fmaf(xs[i], w[i], d0);
+        float d = (d0 + d1) + (d2 + d3);
 #pragma unroll
         for (int s = 16; s > 0; s >>= 1) d += __shfl_xor_sync(0xffffffffu, d, s);
         if (lane == 0) z[o] = d;
@@ -112,7 +124,8 @@ extern "C" int b200_moe_route(const void* h, int h_dtype, const float* w_router,
     if (n_out > 4096) return B200_EUNSUPPORTED;
     if (n_tokens == 0) return B200_OK;
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem = (size_t)2 * n_out * sizeof(float);
+    const size_t smem = ((size_t)2 * n_out + width) * sizeof(float);
+    if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     if (h_dtype == B200_BF16)
         moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, s>>>((const __nv_bfloat16*)h, w_router, correction, width, n_out, top,
                                                                    scale, chosen, weight);
