@@ -134,6 +134,10 @@ __global__ void __launch_bounds__(256) gemm_grouped_simt_kernel(GG g) {
 // ---- bf16 tensor-core tile: 64 x 64 x 32, 4 warps (2 x 2), each warp 32 x 32 = 2 m16 x 4 n8 fragments -----------
 constexpr int MBK = 32, MPAD = 8;   // smem rows of 40 bf16 (80 B): fragment loads hit distinct banks
 
+__device__ __forceinline__ void gg_ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
 __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -206,10 +210,15 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
             const long long src = arow[r];
             Pack16 z; z.w[0] = z.w[1] = z.w[2] = z.w[3] = 0u;
             ra[i] = (src >= 0 && gk < K) ? load8_bf16<TA>(A + src * g.lda + gk) : z;
-            const int gn = n0 + r;
-            const bool ok = gn < N && gk < K;
-            rb[i] = ok ? ld16(W + (long long)gn * g.ldw + gk) : z;
-            if (GLU) rb[GLU ? 2 + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
+            if (TRANS_B) {
+                const int gn = n0 + r;
+                const bool ok = gn < N && gk < K;
+                rb[i] = ok ? ld16(W + (long long)gn * g.ldw + gk) : z;
+                if (GLU) rb[GLU ? 2 + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
+            } else {   // W [K, N]: packets of 8 along n, transposed on the way into shared memory
+                const int bk = k0 + (c >> 3), gn = n0 + (c & 7) * 8;
+                rb[i] = (bk < K && gn < N) ? ld16(W + (long long)bk * g.ldw + gn) : z;
+            }
         }
     };
     if (VEC) fetch(0);
@@ -219,8 +228,15 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
             for (int i = 0; i < 2; ++i) {
                 const int c = threadIdx.x + i * 128, r = c >> 2, kc = (c & 3) * 8;
                 st16(&As[r][kc], ra[i]);
-                st16(&Bs[0][r][kc], rb[i]);
-                if (GLU) st16(&Bs[GLU ? 1 : 0][r][kc], rb[GLU ? 2 + i : 0]);
+                if (TRANS_B) {
+                    st16(&Bs[0][r][kc], rb[i]);
+                    if (GLU) st16(&Bs[GLU ? 1 : 0][r][kc], rb[GLU ? 2 + i : 0]);
+                } else {
+                    const int bk = c >> 3, nc = (c & 7) * 8;
+                    const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&rb[i]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) Bs[0][nc + j][bk] = e[j];
+                }
             }
             __syncthreads();
             if (k0 + MBK < K) fetch(k0 + MBK);
@@ -250,28 +266,27 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
         }
 #pragma unroll
         for (int ks = 0; ks < MBK; ks += 16) {
+            // fragments by ldmatrix: one x4 per 16 x 16 block of A, one x4 per pair of n8 tiles of B
             uint32_t a[2][4];
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                const int r = wm + i * 16 + gid;
-                a[i][0] = *reinterpret_cast<const uint32_t*>(&As[r][ks + tig * 2]);
-                a[i][1] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + tig * 2]);
-                a[i][2] = *reinterpret_cast<const uint32_t*>(&As[r][ks + 8 + tig * 2]);
-                a[i][3] = *reinterpret_cast<const uint32_t*>(&As[r + 8][ks + 8 + tig * 2]);
-            }
+            for (int i = 0; i < 2; ++i)
+                gg_ldsm_x4(a[i], &As[wm + i * 16 + (lane & 7) + ((lane >> 3) & 1) * 8][ks + (lane >> 4) * 8]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int c = wn + j * 8 + gid;
-                uint32_t b[2];
-                b[0] = *reinterpret_cast<const uint32_t*>(&Bs[0][c][ks + tig * 2]);
-                b[1] = *reinterpret_cast<const uint32_t*>(&Bs[0][c][ks + 8 + tig * 2]);
-                mma_bf16(acc[0][j], a[0], b);
-                mma_bf16(acc[1][j], a[1], b);
+            for (int j = 0; j < 4; j += 2) {
+                uint32_t b4[4];
+                gg_ldsm_x4(b4, &Bs[0][wn + j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8][ks + ((lane >> 3) & 1) * 8]);
+                const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+                mma_bf16(acc[0][j], a[0], b0);
+                mma_bf16(acc[1][j], a[1], b0);
+                mma_bf16(acc[0][j + 1], a[0], b1);
+                mma_bf16(acc[1][j + 1], a[1], b1);
                 if (GLU) {
-                    b[0] = *reinterpret_cast<const uint32_t*>(&Bs[GLU ? 1 : 0][c][ks + tig * 2]);
-                    b[1] = *reinterpret_cast<const uint32_t*>(&Bs[GLU ? 1 : 0][c][ks + 8 + tig * 2]);
-                    mma_bf16(acc2[0][j], a[0], b);
-                    mma_bf16(acc2[GLU ? 1 : 0][j], a[1], b);
+                    gg_ldsm_x4(b4, &Bs[GLU ? 1 : 0][wn + j * 8 + (lane & 7) + ((lane >> 4) & 1) * 8][ks + ((lane >> 3) & 1) * 8]);
+                    const uint32_t u0[2] = {b4[0], b4[1]}, u1[2] = {b4[2], b4[3]};
+                    mma_bf16(acc2[0][j], a[0], u0);
+                    mma_bf16(acc2[GLU ? 1 : 0][j], a[1], u0);
+                    mma_bf16(acc2[0][GLU ? j + 1 : 0], a[0], u1);
+                    mma_bf16(acc2[GLU ? 1 : 0][GLU ? j + 1 : 0], a[1], u1);
                 }
             }
         }
@@ -304,8 +319,8 @@ static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) 
 template <typename TA, typename TC>
 static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
-    const bool vec = trans_b && g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
-                     al(g.A, sizeof(TA) * 8) && al(g.W, 16);
+    const bool vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
+                     al(g.A, sizeof(TA) * 8) && al(g.W, 16) && (trans_b || g.N % 8 == 0);
     if (g.epi == B200_GG_GLU) {
         if (!trans_b) return B200_EUNSUPPORTED;
         if (vec) gemm_grouped_mma_kernel<TA, TC, true, true, true><<<grid, 128, 0, s>>>(g);
@@ -313,8 +328,10 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     } else if (trans_b) {
         if (vec) gemm_grouped_mma_kernel<TA, TC, true, false, true><<<grid, 128, 0, s>>>(g);
         else gemm_grouped_mma_kernel<TA, TC, true, false><<<grid, 128, 0, s>>>(g);
-    } else
-        gemm_grouped_mma_kernel<TA, TC, false, false><<<grid, 128, 0, s>>>(g);
+    } else {
+        if (vec) gemm_grouped_mma_kernel<TA, TC, false, false, true><<<grid, 128, 0, s>>>(g);
+        else gemm_grouped_mma_kernel<TA, TC, false, false><<<grid, 128, 0, s>>>(g);
+    }
     return (int)cudaGetLastError();
 }
 

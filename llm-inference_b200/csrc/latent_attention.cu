@@ -154,9 +154,9 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
     const int rpad = (rank + 15) & ~15, RS = rpad + 8;           // smem row stride in elements (16-byte multiple)
     bf* Qs = reinterpret_cast<bf*>(smraw);                        // [32][RS]
     bf* Ks = Qs + kTileRows * RS;                                 // [64][RS]
-    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [32][68]
-    bf* Ps = reinterpret_cast<bf*>(Ss + kTileRows * 68);          // [32][72]
-    float* alpha_s = reinterpret_cast<float*>(Ps + kTileRows * 72);   // [32]
+    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [32][68] scores
+    bf* Ps = reinterpret_cast<bf*>(Ss);                           // [32][136]: a row's probabilities overwrite its own scores
+    float* alpha_s = Ss + kTileRows * 68;                         // [32]
     float* linv_s = alpha_s + kTileRows;                          // [32]
     int* row_pos = reinterpret_cast<int*>(linv_s + kTileRows);    // [32]: position of the row's token, -1 = inactive
 
@@ -228,10 +228,13 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
             {   // ---- scores of keys [8 warp, 8 warp + 8)
                 float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 const bf* krow = Ks + (warp * 8 + gid) * RS + tig * 2;
+                const bf* q0 = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8;
+                const bf* q1 = q0 + 16 * RS;
+#pragma unroll 2
                 for (int ks = 0; ks < rpad; ks += 16) {
                     uint32_t a0[4], a1[4], b[2];
-                    ldsm_x4(a0, Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks + (lane >> 4) * 8);
-                    ldsm_x4(a1, Qs + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks + (lane >> 4) * 8);
+                    ldsm_x4(a0, q0 + ks);
+                    ldsm_x4(a1, q1 + ks);
                     b[0] = *reinterpret_cast<const uint32_t*>(krow + ks);
                     b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 8);
                     mma_bf16_16816(s[0], a0, b);
@@ -262,8 +265,8 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
                 const float al = expf(m_run[i] - mn);
                 l_run[i] = l_run[i] * al + sum;
                 m_run[i] = mn;
-                Ps[r * 72 + lane] = __float2bfloat16_rn(pa);
-                Ps[r * 72 + lane + 32] = __float2bfloat16_rn(pb);
+                Ps[r * 136 + lane] = __float2bfloat16_rn(pa);      // after every lane has read its scores (the shuffles above)
+                Ps[r * 136 + lane + 32] = __float2bfloat16_rn(pb);
                 if (lane == 0) alpha_s[r] = al;
             }
             __syncthreads();
@@ -277,8 +280,8 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
 #pragma unroll
                 for (int kk = 0; kk < kTileKeys; kk += 16) {
                     uint32_t p0[4], p1[4];
-                    ldsm_x4(p0, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
-                    ldsm_x4(p1, Ps + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
+                    ldsm_x4(p0, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 136 + kk + (lane >> 4) * 8);
+                    ldsm_x4(p1, Ps + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 136 + kk + (lane >> 4) * 8);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         const int tile = tile0 + nt;
@@ -397,7 +400,7 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
         // every entry a single token (a decode batch): one token per CTA, its heads the only rows
         const int HG = heads < kTileRows ? heads : kTileRows, TQ = longest_entry == 1 ? 1 : kTileRows / HG;
         const int rpad = (rank + 15) & ~15, RS = rpad + 8;
-        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + kTileRows * 68 * 4 + kTileRows * 72 * 2 + 3 * kTileRows * 4;
+        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + kTileRows * 68 * 4 + 3 * kTileRows * 4;
         const int ntw = (rpad / 8 + kTileWarps - 1) / kTileWarps;
         dim3 tg((n_tokens + TQ - 1) / TQ, (heads + HG - 1) / HG);
         // few CTAs over long contexts (decoding): shares of the key tiles on blockIdx.z, merged by the combine kernel
