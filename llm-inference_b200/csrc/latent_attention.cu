@@ -141,7 +141,7 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 }
 
 template <int NT>   // n8 column tiles of the output per warp: padded rank <= 64 * NT
-__global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __restrict__ qa, float* __restrict__ out,
+__global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* __restrict__ qa, float* __restrict__ out,
                                                                const __nv_bfloat16* __restrict__ pool, const int* __restrict__ pages,
                                                                int max_pages, int page_rows, const int* __restrict__ slot,
                                                                const int* __restrict__ pos, const float* __restrict__ sink, float scale,
@@ -206,13 +206,19 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
             __syncthreads();   // Ks / Ps / Ss of the previous tile are no longer read
             if ((rank & 7) == 0) {
                 const int chunks = rpad / 8;
+                // pages of 64 rows: a tile is exactly one page (k0 is a multiple of 64), so its list entry is read once
+                // and the row loads do not wait on a lookup of their own
+                const bool one_page = page_rows == kTileKeys;
+                const size_t page_base = one_page ? (size_t)list[k0 / kTileKeys] * kTileKeys : 0;
                 for (int i = threadIdx.x; i < kTileKeys * chunks; i += blockDim.x) {
                     const int kr = i / chunks, ch = i - kr * chunks;
                     const int j = k0 + kr;
                     Pack16 v{};
                     v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
-                    if (j < n_keys && ch * 8 < rank)
-                        v = ld16(pool + ((size_t)list[j / page_rows] * page_rows + j % page_rows) * rank + ch * 8);
+                    if (j < n_keys && ch * 8 < rank) {
+                        const size_t row = one_page ? page_base + kr : (size_t)list[j / page_rows] * page_rows + j % page_rows;
+                        v = ld16(pool + row * rank + ch * 8);
+                    }
                     st16(Ks + kr * RS + ch * 8, v);
                 }
             } else {
@@ -226,12 +232,12 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
             }
             __syncthreads();
             {   // ---- scores of keys [8 warp, 8 warp + 8)
-                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                // two independent accumulator sets over alternating k steps (more would cost the second CTA per SM)
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
                 const bf* krow = Ks + (warp * 8 + gid) * RS + tig * 2;
                 const bf* q0 = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8;
                 const bf* q1 = q0 + 16 * RS;
-#pragma unroll 2
-                for (int ks = 0; ks < rpad; ks += 16) {
+                for (int ks = 0; ks < rpad; ks += 32) {
                     uint32_t a0[4], a1[4], b[2];
                     ldsm_x4(a0, q0 + ks);
                     ldsm_x4(a1, q1 + ks);
@@ -239,7 +245,19 @@ __global__ void __launch_bounds__(256) latent_attn_tile_kernel(const float* __re
                     b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 8);
                     mma_bf16_16816(s[0], a0, b);
                     mma_bf16_16816(s[1], a1, b);
+                    if (ks + 16 < rpad) {
+                        ldsm_x4(a0, q0 + ks + 16);
+                        ldsm_x4(a1, q1 + ks + 16);
+                        b[0] = *reinterpret_cast<const uint32_t*>(krow + ks + 16);
+                        b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 24);
+                        mma_bf16_16816(s2[0], a0, b);
+                        mma_bf16_16816(s2[1], a1, b);
+                    }
                 }
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[mt][c] += s2[mt][c];
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
                     float* d0 = Ss + (mt * 16 + gid) * 68 + warp * 8 + tig * 2;
