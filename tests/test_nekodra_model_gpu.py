@@ -30,6 +30,12 @@ SHAPES = {
     "wide": dict(width=96, vocab=50, layers=[
         dict(heads=2, dim=32, vdim=16, kv_rank=136, scale=0.18,
              mlp=dict(kind="moe", expert=dict(ff=8), router=dict(experts=0, identity=4, top=2, scale=1.0), shared=dict(ff=40)))]),
+    # nothing a multiple of 8: every vector path has to fall back; more heads than one attention tile has rows
+    "ragged": dict(width=36, vocab=41, layers=[
+        dict(heads=3, dim=5, vdim=7, kv_rank=12, scale=0.45,
+             mlp=dict(kind="moe", expert=dict(ff=10), router=dict(experts=3, identity=1, top=2, scale=1.5), shared=dict(ff=6))),
+        dict(heads=40, dim=3, vdim=2, kv_rank=12, scale=0.6, kv_from=0,
+             mlp=dict(kind="moe", expert=dict(ff=7), router=dict(experts=2, identity=2, top=3, scale=0.75), shared=dict(ff=9)))]),
 }
 RTOL = {"f32": 2e-4, "bf16": 6e-2}
 
@@ -115,7 +121,7 @@ def test_the_sink_and_the_correction_reach_the_logits(models):
 
 
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
-@pytest.mark.parametrize("name", ["pair", "odd"])
+@pytest.mark.parametrize("name", ["pair", "odd", "ragged"])
 def test_prefill_then_token_by_token_across_page_borders(S, models, name, kind):
     folder, oracle, cfg = models[name]
     m = open_model(S, folder, kind)
