@@ -160,12 +160,15 @@ template <> __device__ __forceinline__ Pack16 load8_bf16<float>(const float* p) 
 
 // VEC: every row of A and W starts on a 16-byte boundary (32 for fp32 A) and K % 8 == 0: 16-byte global loads, the next
 // k tile fetched into registers while the tensor cores work on the current one
-template <typename TA, typename TC, bool TRANS_B, bool GLU, bool VEC = false>
-__global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
+// BM: rows per CTA, 64 (4 warps) or 128 (8 warps: the weight tile is read half as often, twice the MMAs per barrier)
+template <typename TA, typename TC, bool TRANS_B, bool GLU, bool VEC = false, int BM = 64>
+__global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
+    constexpr int NT = BM * 2;        // threads
+    constexpr int NB = 256 / NT;      // 16-byte packets of the W tile per thread
     using bf = __nv_bfloat16;
-    __shared__ __align__(16) bf As[GBM][MBK + MPAD];
+    __shared__ __align__(16) bf As[BM][MBK + MPAD];
     __shared__ __align__(16) bf Bs[GLU ? 2 : 1][GBN][MBK + MPAD];   // [n][k] (k contiguous) whatever W's layout
-    __shared__ long long arow[GBM];
+    __shared__ long long arow[BM];
     const int z = blockIdx.z;
     long long row0 = 0;
     int M = g.M;
@@ -181,7 +184,7 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
         C += (size_t)z * g.sC;
         aux_off = (long long)z * g.s_aux;
     }
-    const int m0 = blockIdx.y * GBM, n0 = blockIdx.x * GBN;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * GBN;
     if (m0 >= M) return;
     const int N = g.N, K = g.K;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
@@ -194,27 +197,31 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
         for (int j = 0; j < 4; ++j)
 #pragma unroll
             for (int k = 0; k < 4; ++k) { acc[i][j][k] = 0.f; if (GLU) acc2[i][j][k] = 0.f; }
-    if (threadIdx.x < GBM) {
+    if (threadIdx.x < BM) {
         const int r = m0 + threadIdx.x;
         long long src = -1;
         if (r < M) src = g.a_rows ? (long long)g.a_rows[row0 + r] : row0 + r;
         arow[threadIdx.x] = src;
     }
     __syncthreads();
-    // VEC: 64 rows x 32 k = 256 packets of 8 per operand tile, two per thread
-    Pack16 ra[2], rb[GLU ? 4 : 2];
+    // VEC: BM rows x 32 k = 4 BM packets of 8 for A (two per thread), 256 packets for the W tile (NB per thread)
+    Pack16 ra[2], rb[GLU ? 2 * NB : NB];
     auto fetch = [&](int k0) {
+        Pack16 z; z.w[0] = z.w[1] = z.w[2] = z.w[3] = 0u;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int c = threadIdx.x + i * 128, r = c >> 2, gk = k0 + (c & 3) * 8;
+            const int c = threadIdx.x + i * NT, r = c >> 2, gk = k0 + (c & 3) * 8;
             const long long src = arow[r];
-            Pack16 z; z.w[0] = z.w[1] = z.w[2] = z.w[3] = 0u;
             ra[i] = (src >= 0 && gk < K) ? load8_bf16<TA>(A + src * g.lda + gk) : z;
+        }
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int c = threadIdx.x + i * NT;
             if (TRANS_B) {
-                const int gn = n0 + r;
+                const int gn = n0 + (c >> 2), gk = k0 + (c & 3) * 8;
                 const bool ok = gn < N && gk < K;
                 rb[i] = ok ? ld16(W + (long long)gn * g.ldw + gk) : z;
-                if (GLU) rb[GLU ? 2 + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
+                if (GLU) rb[GLU ? NB + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
             } else {   // W [K, N]: packets of 8 along n, transposed on the way into shared memory
                 const int bk = k0 + (c >> 3), gn = n0 + (c & 7) * 8;
                 rb[i] = (bk < K && gn < N) ? ld16(W + (long long)bk * g.ldw + gn) : z;
@@ -226,11 +233,15 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
         if (VEC) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                const int c = threadIdx.x + i * 128, r = c >> 2, kc = (c & 3) * 8;
-                st16(&As[r][kc], ra[i]);
+                const int c = threadIdx.x + i * NT;
+                st16(&As[c >> 2][(c & 3) * 8], ra[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < NB; ++i) {
+                const int c = threadIdx.x + i * NT;
                 if (TRANS_B) {
-                    st16(&Bs[0][r][kc], rb[i]);
-                    if (GLU) st16(&Bs[GLU ? 1 : 0][r][kc], rb[GLU ? 2 + i : 0]);
+                    st16(&Bs[0][c >> 2][(c & 3) * 8], rb[i]);
+                    if (GLU) st16(&Bs[GLU ? 1 : 0][c >> 2][(c & 3) * 8], rb[GLU ? NB + i : 0]);
                 } else {
                     const int bk = c >> 3, nc = (c & 7) * 8;
                     const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&rb[i]);
@@ -241,14 +252,14 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
             __syncthreads();
             if (k0 + MBK < K) fetch(k0 + MBK);
         } else {
-        for (int i = threadIdx.x; i < GBM * MBK; i += 128) {
+        for (int i = threadIdx.x; i < BM * MBK; i += NT) {
             const int r = i / MBK, kk = i - r * MBK;
             const int gk = k0 + kk;
             const long long src = arow[r];
             As[r][kk] = (src >= 0 && gk < K) ? __float2bfloat16_rn(DT<TA>::to_f(A[src * g.lda + gk])) : __float2bfloat16_rn(0.f);
         }
         if (TRANS_B) {
-            for (int i = threadIdx.x; i < GBN * MBK; i += 128) {
+            for (int i = threadIdx.x; i < GBN * MBK; i += NT) {
                 const int c = i / MBK, kk = i - c * MBK;
                 const int gn = n0 + c, gk = k0 + kk;
                 const bool ok = gn < N && gk < K;
@@ -256,7 +267,7 @@ __global__ void __launch_bounds__(128) gemm_grouped_mma_kernel(GG g) {
                 if (GLU) Bs[GLU ? 1 : 0][c][kk] = ok ? W[(long long)(gn + N) * g.ldw + gk] : __float2bfloat16_rn(0.f);
             }
         } else {
-            for (int i = threadIdx.x; i < GBN * MBK; i += 128) {
+            for (int i = threadIdx.x; i < GBN * MBK; i += NT) {
                 const int kk = i / GBN, c = i - kk * GBN;
                 const int gn = n0 + c, gk = k0 + kk;
                 Bs[0][c][kk] = (gn < N && gk < K) ? W[(long long)gk * g.ldw + gn] : __float2bfloat16_rn(0.f);
@@ -316,22 +327,30 @@ static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) 
         gemm_grouped_simt_kernel<TA, TW, TC, false, false><<<grid, 256, 0, s>>>(g);
     return (int)cudaGetLastError();
 }
+template <typename TA, typename TC, bool TRANS_B, bool GLU>
+static void gg_launch_mma_tile(const GG& g, dim3 grid, bool vec, bool tall, cudaStream_t s) {
+    if (tall) {
+        grid.y = (grid.y + 1) / 2;
+        if (vec) gemm_grouped_mma_kernel<TA, TC, TRANS_B, GLU, true, 128><<<grid, 256, 0, s>>>(g);
+        else gemm_grouped_mma_kernel<TA, TC, TRANS_B, GLU, false, 128><<<grid, 256, 0, s>>>(g);
+    } else {
+        if (vec) gemm_grouped_mma_kernel<TA, TC, TRANS_B, GLU, true, 64><<<grid, 128, 0, s>>>(g);
+        else gemm_grouped_mma_kernel<TA, TC, TRANS_B, GLU, false, 64><<<grid, 128, 0, s>>>(g);
+    }
+}
 template <typename TA, typename TC>
 static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     auto al = [](const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; };
     const bool vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
                      al(g.A, sizeof(TA) * 8) && al(g.W, 16) && (trans_b || g.N % 8 == 0);
+    const bool tall = g.M > 64;   // the grid was sized for 64-row tiles (M is the row bound of a group)
     if (g.epi == B200_GG_GLU) {
         if (!trans_b) return B200_EUNSUPPORTED;
-        if (vec) gemm_grouped_mma_kernel<TA, TC, true, true, true><<<grid, 128, 0, s>>>(g);
-        else gemm_grouped_mma_kernel<TA, TC, true, true><<<grid, 128, 0, s>>>(g);
-    } else if (trans_b) {
-        if (vec) gemm_grouped_mma_kernel<TA, TC, true, false, true><<<grid, 128, 0, s>>>(g);
-        else gemm_grouped_mma_kernel<TA, TC, true, false><<<grid, 128, 0, s>>>(g);
-    } else {
-        if (vec) gemm_grouped_mma_kernel<TA, TC, false, false, true><<<grid, 128, 0, s>>>(g);
-        else gemm_grouped_mma_kernel<TA, TC, false, false><<<grid, 128, 0, s>>>(g);
-    }
+        gg_launch_mma_tile<TA, TC, true, true>(g, grid, vec, tall, s);
+    } else if (trans_b)
+        gg_launch_mma_tile<TA, TC, true, false>(g, grid, vec, tall, s);
+    else
+        gg_launch_mma_tile<TA, TC, false, false>(g, grid, vec, tall, s);
     return (int)cudaGetLastError();
 }
 
