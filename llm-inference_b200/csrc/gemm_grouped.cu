@@ -10,7 +10,8 @@
 //                            never stored)
 // Element types: A and W float or bfloat16 (any mix), C float or bfloat16; accumulation is fp32 FMA in k order, so a
 // row's result does not depend on which other rows share the launch. Two kernels behind the entry point:
-//   gemm_grouped_mma_kernel  : bf16 operands (A converted on load), mma.sync m16n8k16, 64 x 64 x 32 tiles
+//   gemm_grouped_mma_kernel  : bf16 operands (A converted on load), mma.sync m16n8k16, 64 or 128 x 64 x 64 tiles,
+//                              ldmatrix fragments, 16-byte loads staged through registers one k tile ahead
 //   gemm_grouped_simt_kernel : every combination, true fp32 products (the float32 serving mode)
 #include <cuda_bf16.h>
 
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(256) gemm_grouped_simt_kernel(GG g) {
 }
 
 // ---- bf16 tensor-core tile: 64 x 64 x 32, 4 warps (2 x 2), each warp 32 x 32 = 2 m16 x 4 n8 fragments -----------
-constexpr int MBK = 32, MPAD = 8;   // smem rows of 40 bf16 (80 B): fragment loads hit distinct banks
+constexpr int MBK = 64, MPAD = 8;   // smem rows of 72 bf16 (144 B): ldmatrix rows fall into distinct 16-byte bank groups
+constexpr int CPR = MBK / 8;        // 16-byte packets per tile row
 
 __device__ __forceinline__ void gg_ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -164,7 +166,8 @@ template <> __device__ __forceinline__ Pack16 load8_bf16<float>(const float* p) 
 template <typename TA, typename TC, bool TRANS_B, bool GLU, bool VEC = false, int BM = 64>
 __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
     constexpr int NT = BM * 2;        // threads
-    constexpr int NB = 256 / NT;      // 16-byte packets of the W tile per thread
+    constexpr int NA = BM * CPR / NT;      // 16-byte packets of the A tile per thread
+    constexpr int NB = GBN * CPR / NT;     // ... of the W tile
     using bf = __nv_bfloat16;
     __shared__ __align__(16) bf As[BM][MBK + MPAD];
     __shared__ __align__(16) bf Bs[GLU ? 2 : 1][GBN][MBK + MPAD];   // [n][k] (k contiguous) whatever W's layout
@@ -204,13 +207,13 @@ __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
         arow[threadIdx.x] = src;
     }
     __syncthreads();
-    // VEC: BM rows x 32 k = 4 BM packets of 8 for A (two per thread), 256 packets for the W tile (NB per thread)
-    Pack16 ra[2], rb[GLU ? 2 * NB : NB];
+    // VEC: BM x MBK / 8 packets of 8 for A (NA per thread), GBN x MBK / 8 for the W tile (NB per thread)
+    Pack16 ra[NA], rb[GLU ? 2 * NB : NB];
     auto fetch = [&](int k0) {
         Pack16 z; z.w[0] = z.w[1] = z.w[2] = z.w[3] = 0u;
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int c = threadIdx.x + i * NT, r = c >> 2, gk = k0 + (c & 3) * 8;
+        for (int i = 0; i < NA; ++i) {
+            const int c = threadIdx.x + i * NT, r = c / CPR, gk = k0 + (c % CPR) * 8;
             const long long src = arow[r];
             ra[i] = (src >= 0 && gk < K) ? load8_bf16<TA>(A + src * g.lda + gk) : z;
         }
@@ -218,7 +221,7 @@ __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
         for (int i = 0; i < NB; ++i) {
             const int c = threadIdx.x + i * NT;
             if (TRANS_B) {
-                const int gn = n0 + (c >> 2), gk = k0 + (c & 3) * 8;
+                const int gn = n0 + c / CPR, gk = k0 + (c % CPR) * 8;
                 const bool ok = gn < N && gk < K;
                 rb[i] = ok ? ld16(W + (long long)gn * g.ldw + gk) : z;
                 if (GLU) rb[GLU ? NB + i : 0] = ok ? ld16(W + (long long)(gn + N) * g.ldw + gk) : z;
@@ -232,16 +235,16 @@ __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
     for (int k0 = 0; k0 < K; k0 += MBK) {
         if (VEC) {
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < NA; ++i) {
                 const int c = threadIdx.x + i * NT;
-                st16(&As[c >> 2][(c & 3) * 8], ra[i]);
+                st16(&As[c / CPR][(c % CPR) * 8], ra[i]);
             }
 #pragma unroll
             for (int i = 0; i < NB; ++i) {
                 const int c = threadIdx.x + i * NT;
                 if (TRANS_B) {
-                    st16(&Bs[0][c >> 2][(c & 3) * 8], rb[i]);
-                    if (GLU) st16(&Bs[GLU ? 1 : 0][c >> 2][(c & 3) * 8], rb[GLU ? NB + i : 0]);
+                    st16(&Bs[0][c / CPR][(c % CPR) * 8], rb[i]);
+                    if (GLU) st16(&Bs[GLU ? 1 : 0][c / CPR][(c % CPR) * 8], rb[GLU ? NB + i : 0]);
                 } else {
                     const int bk = c >> 3, nc = (c & 7) * 8;
                     const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&rb[i]);
