@@ -117,14 +117,16 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const float* __restric
 
 // ---- bf16 tensor-core form ---------------------------------------------------------------------------------------
 // One CTA = 32 rows of (token, head) pairs: TQ consecutive tokens of the packed batch x HG heads (all heads share the
-// cached rows, so a row tile staged once serves HG heads). 8 warps. Per tile of 64 cached rows:
-//   S = Q C^T   : warp w computes the 8 keys [8w, 8w+8) for all 32 rows (k over the padded rank), scores to smem
+// cached rows, so a row tile staged once serves HG heads). 8 warps. Per half tile of 32 cached rows (two buffers: the
+// next half arrives by cp.async while this one is used):
+//   S = Q C^T   : warp w computes the 8 keys [8 (w & 3), +8) for all 32 rows over its half of the padded rank; the two
+//                 partial scores go to smem and are added in the softmax
 //   softmax     : warp w owns rows [4w, 4w+4): mask, running max / sum (fp32), P as bf16 to smem, rescale factors
 //   O += P C    : warp w owns output columns [64w', ...) of all 32 rows; the SAME smem tile is the B operand, read
 //                 transposed with ldmatrix.trans
 // The sink enters as the initial state (m = sink, l = 1, O = 0): a virtual row with a zero value.
 // Tokens of different sequences inside one CTA (entry borders, decode batches) are walked segment by segment.
-constexpr int kTileRows = 32, kTileKeys = 64, kTileWarps = 8, kMaxSplits = 16;
+constexpr int kTileRows = 32, kTileKeys = 64, kHalfKeys = 32, kTileWarps = 8, kMaxSplits = 16;
 
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
@@ -153,10 +155,10 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
     extern __shared__ __align__(16) unsigned char smraw[];
     const int rpad = (rank + 15) & ~15, RS = rpad + 8;           // smem row stride in elements (16-byte multiple)
     bf* Qs = reinterpret_cast<bf*>(smraw);                        // [32][RS]
-    bf* Ks = Qs + kTileRows * RS;                                 // [64][RS]
-    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [32][68] scores
-    bf* Ps = reinterpret_cast<bf*>(Ss);                           // [32][136]: a row's probabilities overwrite its own scores
-    float* alpha_s = Ss + kTileRows * 68;                         // [32]
+    bf* Ks = Qs + kTileRows * RS;                                 // [2][32][RS]: half tiles, one being filled while the other is used
+    float* Ss = reinterpret_cast<float*>(Ks + kTileKeys * RS);    // [2][32][36]: partial scores of the two halves of the rank
+    bf* Ps = reinterpret_cast<bf*>(Ss);                           // [32][72]: a row's probabilities overwrite its own scores
+    float* alpha_s = Ss + 2 * kTileRows * 36;                     // [32]
     float* linv_s = alpha_s + kTileRows;                          // [32]
     int* row_pos = reinterpret_cast<int*>(linv_s + kTileRows);    // [32]: position of the row's token, -1 = inactive
 
@@ -202,42 +204,51 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
 #pragma unroll
                 for (int c = 0; c < 4; ++c) o[a][b][c] = 0.f;
 
-        for (int k0 = key_lo; k0 < n_keys; k0 += kTileKeys) {
-            __syncthreads();   // Ks / Ps / Ss of the previous tile are no longer read
-            if ((rank & 7) == 0) {
-                const int chunks = rpad / 8;
-                // pages of 64 rows: a tile is exactly one page (k0 is a multiple of 64), so its list entry is read once
-                // and the row loads do not wait on a lookup of their own
-                const bool one_page = page_rows == kTileKeys;
-                const size_t page_base = one_page ? (size_t)list[k0 / kTileKeys] * kTileKeys : 0;
-                for (int i = threadIdx.x; i < kTileKeys * chunks; i += blockDim.x) {
+        // half tiles of 32 cached rows, double-buffered: the rows of half i + 1 arrive (cp.async, 16 bytes each, zero-filled
+        // beyond the context and in the padding columns) while half i is scored, normalised and accumulated
+        const bool vec = (rank & 7) == 0;
+        const int chunks = rpad / 8;
+        auto load_half = [&](int k0, bf* dstbuf) {
+            if (vec) {
+                const bool one_page = page_rows % kHalfKeys == 0;   // a half tile never straddles two pages
+                const size_t page_base = one_page ? (size_t)list[k0 / page_rows] * page_rows + k0 % page_rows : 0;
+                for (int i = threadIdx.x; i < kHalfKeys * chunks; i += blockDim.x) {
                     const int kr = i / chunks, ch = i - kr * chunks;
                     const int j = k0 + kr;
-                    Pack16 v{};
-                    v.w[0] = v.w[1] = v.w[2] = v.w[3] = 0u;
-                    if (j < n_keys && ch * 8 < rank) {
-                        const size_t row = one_page ? page_base + kr : (size_t)list[j / page_rows] * page_rows + j % page_rows;
-                        v = ld16(pool + row * rank + ch * 8);
-                    }
-                    st16(Ks + kr * RS + ch * 8, v);
+                    const bool ok = j < n_keys && ch * 8 < rank;
+                    const size_t row = !ok ? 0 : one_page ? page_base + kr : (size_t)list[j / page_rows] * page_rows + j % page_rows;
+                    const bf* src = ok ? pool + row * rank + ch * 8 : pool;
+                    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(dstbuf + kr * RS + ch * 8);
+                    const int bytes = ok ? 16 : 0;
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
                 }
             } else {
-                for (int i = threadIdx.x; i < kTileKeys * rpad; i += blockDim.x) {
+                for (int i = threadIdx.x; i < kHalfKeys * rpad; i += blockDim.x) {
                     const int kr = i / rpad, c = i - kr * rpad;
                     const int j = k0 + kr;
                     bf v = __float2bfloat16_rn(0.f);
                     if (j < n_keys && c < rank) v = pool[((size_t)list[j / page_rows] * page_rows + j % page_rows) * rank + c];
-                    Ks[kr * RS + c] = v;
+                    dstbuf[kr * RS + c] = v;
                 }
             }
-            __syncthreads();
-            {   // ---- scores of keys [8 warp, 8 warp + 8)
-                // two independent accumulator sets over alternating k steps (more would cost the second CTA per SM)
-                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}}, s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-                const bf* krow = Ks + (warp * 8 + gid) * RS + tig * 2;
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // the rank is split between the warp groups 0-3 and 4-7 in the score phase (k steps of 16)
+        const int ksplit = (rpad / 32) * 16;
+        const int kbeg = warp < 4 ? 0 : ksplit, kend = warp < 4 ? ksplit : rpad;
+        if (key_lo < n_keys) load_half(key_lo, Ks);
+        int buf = 0;
+        for (int k0 = key_lo; k0 < n_keys; k0 += kHalfKeys, buf ^= 1) {
+            bf* Kb = Ks + buf * kHalfKeys * RS;
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();   // half k0 has landed for everybody; the other buffer, Ss and Ps are no longer read
+            if (k0 + kHalfKeys < n_keys) load_half(k0 + kHalfKeys, Ks + (buf ^ 1) * kHalfKeys * RS);
+            {   // ---- partial scores: keys [8 (warp & 3), +8), rank columns [kbeg, kend)
+                float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+                const bf* krow = Kb + ((warp & 3) * 8 + gid) * RS + tig * 2;
                 const bf* q0 = Qs + ((lane & 7) + ((lane >> 3) & 1) * 8) * RS + (lane >> 4) * 8;
                 const bf* q1 = q0 + 16 * RS;
-                for (int ks = 0; ks < rpad; ks += 32) {
+                for (int ks = kbeg; ks < kend; ks += 16) {
                     uint32_t a0[4], a1[4], b[2];
                     ldsm_x4(a0, q0 + ks);
                     ldsm_x4(a1, q1 + ks);
@@ -245,46 +256,33 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
                     b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 8);
                     mma_bf16_16816(s[0], a0, b);
                     mma_bf16_16816(s[1], a1, b);
-                    if (ks + 16 < rpad) {
-                        ldsm_x4(a0, q0 + ks + 16);
-                        ldsm_x4(a1, q1 + ks + 16);
-                        b[0] = *reinterpret_cast<const uint32_t*>(krow + ks + 16);
-                        b[1] = *reinterpret_cast<const uint32_t*>(krow + ks + 24);
-                        mma_bf16_16816(s2[0], a0, b);
-                        mma_bf16_16816(s2[1], a1, b);
-                    }
                 }
-#pragma unroll
-                for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) s[mt][c] += s2[mt][c];
+                float* base = Ss + (warp >> 2) * kTileRows * 36;
 #pragma unroll
                 for (int mt = 0; mt < 2; ++mt) {
-                    float* d0 = Ss + (mt * 16 + gid) * 68 + warp * 8 + tig * 2;
+                    float* d0 = base + (mt * 16 + gid) * 36 + (warp & 3) * 8 + tig * 2;
                     d0[0] = s[mt][0]; d0[1] = s[mt][1];
-                    d0[8 * 68] = s[mt][2]; d0[8 * 68 + 1] = s[mt][3];
+                    d0[8 * 36] = s[mt][2]; d0[8 * 36 + 1] = s[mt][3];
                 }
             }
             __syncthreads();
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {   // ---- softmax of rows [4 warp, 4 warp + 4)
+            for (int i = 0; i < 4; ++i) {   // ---- softmax of rows [4 warp, 4 warp + 4): one key per lane
                 const int r = warp * 4 + i, rp = row_pos[r];
-                const int ka = k0 + lane, kb = k0 + lane + 32;
-                const float sa = ka <= rp ? Ss[r * 68 + lane] * scale : -INFINITY;
-                const float sb = kb <= rp ? Ss[r * 68 + lane + 32] * scale : -INFINITY;
-                float mx = fmaxf(sa, sb);
+                const int ka = k0 + lane;
+                const float sa = ka <= rp ? (Ss[r * 36 + lane] + Ss[(kTileRows + r) * 36 + lane]) * scale : -INFINITY;
+                float mx = sa;
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-                const float mn = fmaxf(m_run[i], mx);           // finite: m starts at the sink
-                const float pa = ka <= rp ? expf(sa - mn) : 0.f, pb = kb <= rp ? expf(sb - mn) : 0.f;
-                float sum = pa + pb;
+                const float mn = fmaxf(m_run[i], mx);           // finite: m starts at the sink (or at -1e30 in a share)
+                const float pa = ka <= rp ? expf(sa - mn) : 0.f;
+                float sum = pa;
 #pragma unroll
                 for (int d = 16; d > 0; d >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, d);
                 const float al = expf(m_run[i] - mn);
                 l_run[i] = l_run[i] * al + sum;
                 m_run[i] = mn;
-                Ps[r * 136 + lane] = __float2bfloat16_rn(pa);      // after every lane has read its scores (the shuffles above)
-                Ps[r * 136 + lane + 32] = __float2bfloat16_rn(pb);
+                Ps[r * 72 + lane] = __float2bfloat16_rn(pa);    // after every lane has read its scores (the shuffles above)
                 if (lane == 0) alpha_s[r] = al;
             }
             __syncthreads();
@@ -296,16 +294,16 @@ __global__ void __launch_bounds__(256, 2) latent_attn_tile_kernel(const float* _
                     for (int nt = 0; nt < NT; ++nt) { o[mt][nt][0] *= a0; o[mt][nt][1] *= a0; o[mt][nt][2] *= a1; o[mt][nt][3] *= a1; }
                 }
 #pragma unroll
-                for (int kk = 0; kk < kTileKeys; kk += 16) {
+                for (int kk = 0; kk < kHalfKeys; kk += 16) {
                     uint32_t p0[4], p1[4];
-                    ldsm_x4(p0, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 136 + kk + (lane >> 4) * 8);
-                    ldsm_x4(p1, Ps + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 136 + kk + (lane >> 4) * 8);
+                    ldsm_x4(p0, Ps + ((lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
+                    ldsm_x4(p1, Ps + (16 + (lane & 7) + ((lane >> 3) & 1) * 8) * 72 + kk + (lane >> 4) * 8);
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         const int tile = tile0 + nt;
                         if (nt < ntw && tile < n8) {
                             uint32_t b[2];
-                            ldsm_x2_trans(b, Ks + (kk + (lane & 15)) * RS + tile * 8);
+                            ldsm_x2_trans(b, Kb + (kk + (lane & 15)) * RS + tile * 8);
                             mma_bf16_16816(o[0][nt], p0, b);
                             mma_bf16_16816(o[1][nt], p1, b);
                         }
@@ -418,7 +416,7 @@ extern "C" int b200_latent_attention(const float* qa, float* out, const void* po
         // every entry a single token (a decode batch): one token per CTA, its heads the only rows
         const int HG = heads < kTileRows ? heads : kTileRows, TQ = longest_entry == 1 ? 1 : kTileRows / HG;
         const int rpad = (rank + 15) & ~15, RS = rpad + 8;
-        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + kTileRows * 68 * 4 + 3 * kTileRows * 4;
+        const size_t tsm = (size_t)(kTileRows + kTileKeys) * RS * 2 + 2 * kTileRows * 36 * 4 + 3 * kTileRows * 4;
         const int ntw = (rpad / 8 + kTileWarps - 1) / kTileWarps;
         dim3 tg((n_tokens + TQ - 1) / TQ, (heads + HG - 1) / HG);
         // few CTAs over long contexts (decoding): shares of the key tiles on blockIdx.z, merged by the combine kernel
