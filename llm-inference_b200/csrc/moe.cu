@@ -7,9 +7,10 @@
 
 namespace b200 {
 
-// one CTA per token: warps compute the router outputs (fp32 dot over the width), thread 0 the softmax and the choice
+// one CTA per token: 16 warps compute the router outputs (fp32 dot over the width, eight loads in flight per lane),
+// thread 0 the softmax and the choice
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
+__global__ void __launch_bounds__(512) moe_route_kernel(const T* __restrict__ h, const float* __restrict__ wr,
                                                         const float* __restrict__ corr, int width, int n_out, int top,
                                                         float scale, int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float z[];   // z[n_out] | pick[n_out] | x[width]
@@ -20,15 +21,23 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const T* __restrict__ h,
     // the token's input once in shared memory as fp32, then four independent partial sums per lane
     for (int i = threadIdx.x; i < width; i += blockDim.x) xs[i] = DT<T>::to_f(x[i]);
     __syncthreads();
-    for (int o = warp; o < n_out; o += 4) {
+    const int nw = blockDim.x / 32;
+    for (int o = warp; o < n_out; o += nw) {
         const float* w = wr + (size_t)o * width;
         float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
         int i = lane;
-        for (; i + 96 < width; i += 128) {
-            d0 = fmaf(xs[i], w[i], d0);
-            d1 = fmaf(xs[i + 32], w[i + 32], d1);
-            d2 = fmaf(xs[i + 64], w[i + 64], d2);
-            d3 = fmaf(xs[i + 96], w[i + 96], d3);
+        for (; i + 224 < width; i += 256) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = w[i + 32 * u];
+            d0 = fmaf(xs[i], v[0], d0);
+            d1 = fmaf(xs[i + 32], v[1], d1);
+            d2 = fmaf(xs[i + 64], v[2], d2);
+            d3 = fmaf(xs[i + 96], v[3], d3);
+            d0 = fmaf(xs[i + 128], v[4], d0);
+            d1 = fmaf(xs[i + 160], v[5], d1);
+            d2 = fmaf(xs[i + 192], v[6], d2);
+            d3 = fmaf(xs[i + 224], v[7], d3);
         }
         for (; i < width; i += 32) d0 = fmaf(xs[i], w[i], d0);
         float d = (d0 + d1) + (d2 + d3);
@@ -127,10 +136,10 @@ extern "C" int b200_moe_route(const void* h, int h_dtype, const float* w_router,
     const size_t smem = ((size_t)2 * n_out + width) * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     if (h_dtype == B200_BF16)
-        moe_route_kernel<__nv_bfloat16><<<n_tokens, 128, smem, s>>>((const __nv_bfloat16*)h, w_router, correction, width, n_out, top,
+        moe_route_kernel<__nv_bfloat16><<<n_tokens, 512, smem, s>>>((const __nv_bfloat16*)h, w_router, correction, width, n_out, top,
                                                                    scale, chosen, weight);
     else if (h_dtype == B200_F32)
-        moe_route_kernel<float><<<n_tokens, 128, smem, s>>>((const float*)h, w_router, correction, width, n_out, top, scale, chosen,
+        moe_route_kernel<float><<<n_tokens, 512, smem, s>>>((const float*)h, w_router, correction, width, n_out, top, scale, chosen,
                                                            weight);
     else
         return B200_EINVAL;
