@@ -11,6 +11,8 @@ Workloads (BASELINE.json configs):
   cfg5: LLaMA-2-70B-shaped GQA (64 q / 8 kv heads, 80 layers) fp16 decode, tensor parallel over the N GPUs
         (strong scaling: heads / FFN columns split, allreduce after o_proj and down_proj only);
         --comm p2p = the fused one-shot NVLink allreduce + residual kernel, --comm nccl = the NCCL baseline.
+  nekodra: not a BASELINE.json config: prefill and decode tokens/s of the Nekodra family (include/b200_serve.h, random
+        weights, --size s|m) beside the LLaMA engine at equal size; prints a line of its own shape.
   cfg3: prefill, batch 4 x 2048 prompt tokens per GPU (metric prefill_tokens_per_s; a step = one prompt
         pass of the whole model: tcgen05 GEMMs + flash context attention; roofline = tensor).
 `value`  : tokens/s with everything resident in HBM, CUDA events on the engine's stream, max over ranks.

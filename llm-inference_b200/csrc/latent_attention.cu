@@ -10,9 +10,11 @@
 //   latent_store_kernel        RMS norm (eps inside the root) of the down-projected row, times weight -> its page slot
 //   latent_attn_kernel         one CTA per (token, head): the warps walk the visible rows round-robin, each row read
 //                              coalesced by one warp; per-warp online softmax, merged with the sink at the end
-//   latent_attn_tile_kernel    bf16 tensor-core form (mma.sync): one CTA per 32 (token, head) rows; a tile of 64 cached
-//                              rows is staged in shared memory once and is the operand of both the scores and the
-//                              weighted sum (prompt portions and decoded tokens alike; the default for bf16 caches)
+//   latent_attn_tile_kernel    bf16 tensor-core form (mma.sync): one CTA per 32 (token, head) rows; half tiles of 32 cached
+//                              rows arrive in two shared-memory buffers by cp.async and are the operand of both the
+//                              scores and the weighted sum (prompt portions and decoded tokens alike; the default for
+//                              bf16 caches); decode batches split long contexts over several CTAs
+//   latent_attn_combine_kernel merges the shares of a split launch and the sink
 #include <algorithm>
 
 #include "b200_serve.h"
