@@ -6,7 +6,8 @@
  * routing). b200_engine.h stays the LLaMA hot path; b200_model_open wraps it for checkpoints of that family.
  *
  * Families: "Nekodra" (config.json + model.safetensors: parallel layers of latent attention without positions and a
- * routed feed-forward with identity experts), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
+ * routed feed-forward with identity experts), "Musilorn" (sandwich-normed layers of convolved, capped attention with a
+ * sink or of retention with a carried state, a span of layers run several times), "llama" (the reference's weight directory, llama_weights.cc:41-53, with
  * a config.json naming the b200_model_config fields).
  */
 #ifndef B200_SERVE_H
@@ -25,7 +26,8 @@ extern "C" {
  * kernels
  * --------------------------------------------------------------------------------------------- */
 
-/* out[t,:] = table[ids[t],:] + pos_table[pos[t],:] as fp32 (the residual stream is fp32); tables of `dtype` */
+/* out[t,:] = table[ids[t],:] + pos_table[pos[t],:] as fp32 (the residual stream is fp32); tables of `dtype`.
+ * pos_table (and pos) may be NULL: a model without learned positions. */
 int b200_embed_positions(const int* ids, const int* pos, const void* table, const void* pos_table, float* out,
                          int n_tokens, int width, int dtype, void* stream);
 
@@ -40,6 +42,7 @@ int b200_layernorm_pair(const float* x, const int* rows, int n_rows, int width, 
 #define B200_GG_NONE 0
 #define B200_GG_SIGMOID_MUL 1 /* C = acc * sigmoid(aux[row, col])                                   */
 #define B200_GG_GLU 2         /* C = silu(A W[0:N]^T) * (A W[N:2N]^T); W has 2N rows; trans_b only  */
+#define B200_GG_GLU_GELU 3    /* the same with gelu in its tanh form as the activation              */
 
 typedef struct b200_gemm_grouped_args {
     const void* A; const void* W; void* C;
@@ -101,6 +104,91 @@ int b200_moe_dispatch(const int* chosen, int n_tokens, int top, int n_experts, i
  * (fp32 sums in a fixed order; mix, shared, the routed part may each be NULL) */
 int b200_residual_combine(float* x, const float* mix, const float* shared, const float* expert_out, const int* dest,
                           const float* weight, const void* h, int h_dtype, int n_tokens, int width, int top, void* stream);
+
+/* Sandwich layers (a norm before AND after each sublayer): x[t,:] += mult * LN(y[t,:]; w, b) on the fp32 residual, then,
+ * when out2 is given, out2[t,:] = LN(x[t,:]; w2, b2) as out_dtype (the input of the next sublayer) from the same row
+ * while it is still on chip. Two-pass mean / variance in fp32 for both norms. */
+int b200_layernorm_residual(float* x, const float* y, int n_rows, int width, float eps, float mult, const float* w,
+                            const float* b, const float* w2, const float* b2, void* out2, int out_dtype, void* stream);
+/* out[t, 0:width] = a[t,:], out[t, width:2 width] = b[t,:], as out_dtype (the operand of a projection of two streams) */
+int b200_concat_cast(const float* a, const float* b, void* out, int n_rows, int width, int out_dtype, void* stream);
+/* v[i] <- cap * tanh(v[i] / cap) */
+int b200_softcap(float* v, size_t n, float cap, void* stream);
+
+/* Rotary positions: cos_out / sin_out [n_tokens, n_freq] = cos / sin(pos[t] * freq[i]); the angle is formed and reduced in
+ * double precision (freq is a device array of doubles, whatever scaling of the frequencies already applied by the
+ * caller), so position 10^5 is as exact as position 1. One launch per step and frequency set, shared by all layers. */
+int b200_rope_angles(const int* pos, int n_tokens, const double* freq, int n_freq, float* cos_out, float* sin_out, void* stream);
+#define B200_ROPE_HALF 0        /* dimension i pairs with i + dims/2  */
+#define B200_ROPE_INTERLEAVED 1 /* dimension 2i pairs with 2i + 1      */
+
+/* What lies between the q / k projection of an attention layer and its cache, in one launch per token and head:
+ * an optional short causal convolution over time on every channel (y_t = sum_j w[c, j] u_(t - taps + 1 + j), zeros before
+ * position 0; inputs older than this step come from conv_state), an optional per-head RMS norm with a weight shared by
+ * the heads, rotary positions on the first rot_dims dimensions, then q to q_out and k into the page pool. Values:
+ * v_from_conv != 0 stores the convolved, un-normed, un-rotated keys as the values (a design without a value
+ * projection). Everything in fp32 up to the store in `dtype`.
+ * Channels: query heads first, then key heads (proj row = [heads*dim | kv_heads*dim], leading dimension ld_proj).
+ * start[t] = position of the first token that the token's sequence brings in THIS step (older inputs are state).
+ * conv_state: fp32 [n_slots, taps-1, channels], position p at ring place p % (taps-1); written by
+ * b200_conv_state_update AFTER this launch (the same stream), never by this kernel. */
+typedef struct b200_qk_prepare_args {
+    const float* proj; long long ld_proj;
+    const float* conv_w; int taps; const float* conv_state;   /* conv_w NULL: no convolution */
+    const float* q_norm; const float* k_norm; float eps;       /* NULL: no norm               */
+    const float* cos; const float* sin; int rot_dims, rot_layout;
+    void* q_out;                    /* dtype [n_tokens, heads*dim]                                  */
+    void* k_pool; void* v_pool;     /* dtype [n_pages*page_rows, kv_heads, dim]                     */
+    int v_from_conv;
+    const int* pages; int max_pages, page_rows;
+    const int* slot; const int* pos; const int* start;
+    int n_tokens, heads, kv_heads, dim, dtype;
+} b200_qk_prepare_args;
+int b200_qk_prepare(const b200_qk_prepare_args* a, void* stream);
+/* The last taps-1 inputs of every sequence of the step go to their ring places (end[t] = the sequence's length after
+ * the step). */
+int b200_conv_state_update(const float* proj, long long ld_proj, float* conv_state, const int* slot, const int* pos,
+                           const int* end, int n_tokens, int channels, int taps, void* stream);
+
+/* Causal attention over paged per-head keys and values with grouped query heads (query head h reads key head
+ * h / (heads / kv_heads)): s_j = scale * <q, k_j>, then s_j <- softcap * tanh(s_j / softcap) when softcap > 0, over the
+ * sequence's rows j <= pos[t]; p_j = exp(s_j) / (denom_bias + sum_j exp(s_j)) (denom_bias 1: a sink of score 0 without
+ * a value; 0: plain softmax); out[t, h, :] = sum_j p_j v_j. q [n_tokens, heads*dim], out [n_tokens, heads*vdim], pools
+ * [n_pages*page_rows, kv_heads, dim | vdim], all of `dtype`; scores, softmax and sums in fp32.
+ * longest_entry (0 = unknown): most tokens one sequence brings in this batch; bfloat16 batches with prompt portions run
+ * on tensor-core tiles, single tokens and fp32 on the row kernel. */
+typedef struct b200_paged_attention_args {
+    const void* q; void* out; const void* k_pool; const void* v_pool;
+    const int* pages; int max_pages, page_rows;
+    const int* slot; const int* pos;
+    int n_tokens, heads, kv_heads, dim, vdim;
+    float scale, softcap, denom_bias;
+    int dtype, longest_entry;
+} b200_paged_attention_args;
+int b200_paged_attention(const b200_paged_attention_args* a, void* stream);
+
+/* Retention: linear attention with a fixed decay per head and a carried state, no softmax. For every entry (a run of
+ * consecutive tokens of one sequence: first batch row ent_row[e], ent_len[e] tokens) and head h, with q, k rotated on
+ * their first rot_dims dimensions and k multiplied by k_scale after the rotation:
+ *   S <- decay[h] * S + k_t v_t^T,   out[t, h, :] = S^T q_t
+ * S fp32 [n_slots, heads, dim, vdim], starting from zero when the entry starts at position 0 (a slot that is used
+ * again needs no clearing) and left in place for the next step. proj fp32 [n_tokens, ld_proj] holds q at column q_off
+ * (heads*dim), k at k_off, v at v_off (heads*vdim). All arithmetic fp32. out fp32 [n_tokens, heads*vdim]. */
+typedef struct b200_retention_args {
+    const float* proj; long long ld_proj; int q_off, k_off, v_off;
+    const float* cos; const float* sin; int rot_dims, rot_layout;
+    const float* decay; float k_scale;
+    float* state; float* out;
+    const int* ent_row; const int* ent_len; const int* slot; const int* pos;
+    int n_entries, n_tokens, heads, dim, vdim, longest_entry;
+    void* workspace; size_t workspace_bytes;   /* chunk states of long entries (b200_retention_workspace_bytes) */
+} b200_retention_args;
+size_t b200_retention_workspace_bytes(int n_tokens, int n_entries, int heads, int dim, int vdim);
+int b200_retention(const b200_retention_args* a, void* stream);
+/* out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]) as out_dtype (gate fp32, leading
+ * dimension ld_gate) */
+int b200_unit_rms_gate(const float* o, const float* gate, long long ld_gate, void* out, int n_tokens, int heads, int vdim,
+                       float eps, int out_dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * models

@@ -36,6 +36,11 @@ template <> struct DT<__nv_bfloat16> {
     static __device__ __forceinline__ __nv_bfloat16 from_f(float v) { return __float2bfloat16_rn(v); }
 };
 
+// gelu in its tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), fp32 with the accurate tanhf
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
 // 16-byte packet: the unit every bandwidth kernel moves per thread per access.
 struct __align__(16) Pack16 {
     uint32_t w[4];

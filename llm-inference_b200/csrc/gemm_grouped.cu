@@ -34,6 +34,7 @@ template <typename TC>
 __device__ __forceinline__ void gg_store(const GG& g, TC* C, long long row, int col, float v, float v2, long long aux_off) {
     if (g.epi == B200_GG_SIGMOID_MUL) v *= 1.f / (1.f + expf(-g.aux[aux_off + row * g.ld_aux + col]));
     else if (g.epi == B200_GG_GLU) v = v / (1.f + expf(-v)) * v2;
+    else if (g.epi == B200_GG_GLU_GELU) v = gelu_tanh_f(v) * v2;
     C[row * g.ldc + col] = DT<TC>::from_f(v);
 }
 
@@ -321,7 +322,7 @@ __global__ void __launch_bounds__(BM * 2) gemm_grouped_mma_kernel(GG g) {
 
 template <typename TA, typename TW, typename TC>
 static int gg_launch_simt(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
-    if (g.epi == B200_GG_GLU) {
+    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU) {
         if (!trans_b) return B200_EUNSUPPORTED;
         gemm_grouped_simt_kernel<TA, TW, TC, true, true><<<grid, 256, 0, s>>>(g);
     } else if (trans_b)
@@ -347,7 +348,7 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     const bool vec = g.K % 8 == 0 && g.lda % 8 == 0 && g.ldw % 8 == 0 && g.sA % 8 == 0 && g.sW % 8 == 0 &&
                      al(g.A, sizeof(TA) * 8) && al(g.W, 16) && (trans_b || g.N % 8 == 0);
     const bool tall = g.M > 64;   // the grid was sized for 64-row tiles (M is the row bound of a group)
-    if (g.epi == B200_GG_GLU) {
+    if (g.epi == B200_GG_GLU || g.epi == B200_GG_GLU_GELU) {
         if (!trans_b) return B200_EUNSUPPORTED;
         gg_launch_mma_tile<TA, TC, true, true>(g, grid, vec, tall, s);
     } else if (trans_b)
@@ -357,8 +358,8 @@ static int gg_launch_mma(const GG& g, dim3 grid, bool trans_b, cudaStream_t s) {
     return (int)cudaGetLastError();
 }
 
-int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, bool glu, void* workspace,
-                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu
+int gemm_tcgen05_ex(const void* x, const void* W, void* y, int M, int N, int K, int in_bf16, int out_kind, int glu, void* workspace,
+                    size_t workspace_bytes, cudaStream_t s);   // gemm_tcgen05.cu (glu: 0 none, 1 silu, 2 tanh-gelu)
 size_t gemm_tcgen05_ex_workspace_bytes(int M, int N, int K);
 
 static bool mma_enabled() {
@@ -414,10 +415,10 @@ extern "C" size_t b200_linear_ex_workspace_bytes(int n_tokens, int N, int K) {
 
 extern "C" int b200_linear_ex(const void* x, const void* W, void* y, int n_tokens, int N, int K, int in_dtype, int out_dtype, int epi,
                               void* workspace, size_t workspace_bytes, void* stream) {
-    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU)) return B200_EINVAL;
+    if (!x || !W || !y || n_tokens < 0 || N < 1 || K < 1 || (epi != B200_GG_NONE && epi != B200_GG_GLU && epi != B200_GG_GLU_GELU)) return B200_EINVAL;
     if (n_tokens == 0) return B200_OK;
     if (in_dtype == B200_BF16 && (out_dtype == B200_BF16 || out_dtype == B200_F32)) {
-        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU, workspace,
+        const int rc = gemm_tcgen05_ex(x, W, y, n_tokens, N, K, 1, out_dtype == B200_BF16 ? 1 : 2, epi == B200_GG_GLU ? 1 : epi == B200_GG_GLU_GELU ? 2 : 0, workspace,
                                        workspace_bytes, (cudaStream_t)stream);
         if (rc != B200_EUNSUPPORTED) return rc;
     }

@@ -1,4 +1,5 @@
-// Embedding with learned positions and layer norm (weight + bias), beside norm.cu's RMS norms.
+// Embedding (with or without learned positions), layer norm (weight + bias) before a sublayer, and the sandwich form
+// (norm of the sublayer's output added to the residual, then the next sublayer's input norm), beside norm.cu's RMS norms.
 // The residual stream these kernels read and write is fp32; their outputs feed GEMMs and take the serving dtype.
 #include "b200_serve.h"
 #include "common.cuh"
@@ -11,6 +12,10 @@ __global__ void embed_positions_kernel(const int* __restrict__ ids, const int* _
                                        const T* __restrict__ pos_table, float* __restrict__ out, int width) {
     const int t = blockIdx.x;
     const T* e = table + (size_t)ids[t] * width;
+    if (!pos_table) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = DT<T>::to_f(e[i]);
+        return;
+    }
     const T* p = pos_table + (size_t)pos[t] * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = DT<T>::to_f(e[i]) + DT<T>::to_f(p[i]);
 }
@@ -58,13 +63,108 @@ __global__ void __launch_bounds__(256) layernorm_pair_kernel(const float* __rest
     }
 }
 
+// x += mult * LN(y; w, b); out2 = LN(x; w2, b2). One CTA per row; the row of y, then the new row of x, stay in shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_residual_kernel(float* __restrict__ x, const float* __restrict__ y, int width,
+                                                                 float eps, float mult, const float* __restrict__ w,
+                                                                 const float* __restrict__ b, const float* __restrict__ w2,
+                                                                 const float* __restrict__ b2, T* __restrict__ out2) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * width;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = y[base + c];
+        row[c] = v;
+        s += v;
+    }
+    float mean = ln_block_sum(s, red) / (float)width;
+    float q = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float d = row[c] - mean;
+        q += d * d;
+    }
+    float rstd = 1.0f / sqrtf(ln_block_sum(q, red) / (float)width + eps);
+    s = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float v = x[base + c] + mult * ((row[c] - mean) * rstd * w[c] + b[c]);
+        x[base + c] = v;
+        row[c] = v;
+        s += v;
+    }
+    if (!out2) return;
+    mean = ln_block_sum(s, red) / (float)width;
+    q = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float d = row[c] - mean;
+        q += d * d;
+    }
+    rstd = 1.0f / sqrtf(ln_block_sum(q, red) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out2[base + c] = DT<T>::from_f((row[c] - mean) * rstd * w2[c] + b2[c]);
+}
+
+template <typename T>
+__global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int width) {
+    const size_t t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        out[t * 2 * width + c] = DT<T>::from_f(a[t * width + c]);
+        out[t * 2 * width + width + c] = DT<T>::from_f(b[t * width + c]);
+    }
+}
+
+__global__ void softcap_kernel(float* __restrict__ v, size_t n, float cap) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) v[i] = cap * tanhf(v[i] / cap);
+}
+
 }  // namespace b200
 
 using namespace b200;
 
+extern "C" int b200_layernorm_residual(float* x, const float* y, int n_rows, int width, float eps, float mult, const float* w,
+                                       const float* b, const float* w2, const float* b2, void* out2, int out_dtype, void* stream) {
+    if (!x || !y || !w || !b || n_rows < 0 || width < 1) return B200_EINVAL;
+    if (out2 && (!w2 || !b2)) return B200_EINVAL;
+    if (n_rows == 0) return B200_OK;
+    const size_t smem = (size_t)width * sizeof(float);
+    if (smem > 200 * 1024) return B200_EUNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == B200_BF16) {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<__nv_bfloat16>, (int)smem, done);
+        layernorm_residual_kernel<__nv_bfloat16><<<n_rows, 256, smem, s>>>(x, y, width, eps, mult, w, b, w2, b2, (__nv_bfloat16*)out2);
+    } else if (out_dtype == B200_F32) {
+        static unsigned long long done = 0;
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<float>, (int)smem, done);
+        layernorm_residual_kernel<float><<<n_rows, 256, smem, s>>>(x, y, width, eps, mult, w, b, w2, b2, (float*)out2);
+    } else
+        return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_concat_cast(const float* a, const float* b, void* out, int n_rows, int width, int out_dtype, void* stream) {
+    if (!a || !b || !out || n_rows < 0 || width < 1) return B200_EINVAL;
+    if (n_rows == 0) return B200_OK;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == B200_BF16) concat_cast_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>(a, b, (__nv_bfloat16*)out, width);
+    else if (out_dtype == B200_F32) concat_cast_kernel<float><<<n_rows, 256, 0, s>>>(a, b, (float*)out, width);
+    else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_softcap(float* v, size_t n, float cap, void* stream) {
+    if (!v || !(cap > 0.f)) return B200_EINVAL;
+    if (n == 0) return B200_OK;
+    softcap_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(v, n, cap);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
 extern "C" int b200_embed_positions(const int* ids, const int* pos, const void* table, const void* pos_table, float* out,
                                     int n_tokens, int width, int dtype, void* stream) {
-    if (!ids || !pos || !table || !pos_table || !out || n_tokens < 0 || width < 1) return B200_EINVAL;
+    if (!ids || !table || !out || (pos_table && !pos) || n_tokens < 0 || width < 1) return B200_EINVAL;
     if (n_tokens == 0) return B200_OK;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == B200_BF16)

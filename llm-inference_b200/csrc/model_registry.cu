@@ -58,8 +58,8 @@ int SequenceBatch::ensure_capacity(int tokens) {
     if (host_) cudaFreeHost(host_);
     if (dev_) cudaFree(dev_);
     host_ = nullptr; dev_ = nullptr; cap_ = 0;
-    if (cudaMallocHost(&host_, (size_t)4 * cap * sizeof(int)) != cudaSuccess) return B200_ENOMEM;
-    if (cudaMalloc(&dev_, (size_t)4 * cap * sizeof(int)) != cudaSuccess) return B200_ENOMEM;
+    if (cudaMallocHost(&host_, (size_t)kTables * cap * sizeof(int)) != cudaSuccess) return B200_ENOMEM;
+    if (cudaMalloc(&dev_, (size_t)kTables * cap * sizeof(int)) != cudaSuccess) return B200_ENOMEM;
     cap_ = cap;
     return B200_OK;
 }
@@ -96,19 +96,28 @@ int SequenceBatch::begin_step(const std::vector<StepEntry>& entries, cudaStream_
     int* slot = host_ + cap_;
     int* pos = host_ + 2 * (size_t)cap_;
     int* rows = host_ + 3 * (size_t)cap_;
-    int t = 0, w = 0;
+    int* start = host_ + 4 * (size_t)cap_;
+    int* end = host_ + 5 * (size_t)cap_;
+    int* ent_row = host_ + 6 * (size_t)cap_;
+    int* ent_len = host_ + 7 * (size_t)cap_;
+    int t = 0, w = 0, ne = 0;
     for (const StepEntry& en : entries) {
         for (int k = 0; k < en.n_want; ++k) rows[w++] = t + en.want[k];
+        ent_row[ne] = t;
+        ent_len[ne++] = en.n_tokens;
         for (int i = 0; i < en.n_tokens; ++i, ++t) {
             ids[t] = en.tokens[i];
             slot[t] = en.slot;
             pos[t] = length[en.slot] + i;
+            start[t] = length[en.slot];
+            end[t] = length[en.slot] + en.n_tokens;
         }
         length[en.slot] += en.n_tokens;
     }
     n_tokens = total;
+    n_entries = ne;
     n_want = wants;
-    cudaError_t e = cudaMemcpyAsync(dev_, host_, (size_t)4 * cap_ * sizeof(int), cudaMemcpyHostToDevice, stream);
+    cudaError_t e = cudaMemcpyAsync(dev_, host_, (size_t)kTables * cap_ * sizeof(int), cudaMemcpyHostToDevice, stream);
     if (e == cudaSuccess) e = cudaEventRecord(copied_, stream);
     if (e == cudaSuccess && pool.dirty()) e = pool.upload(stream);
     if (e != cudaSuccess) { err = std::string("step: upload: ") + cudaGetErrorString(e); return (int)e; }

@@ -4,6 +4,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -27,7 +28,10 @@ struct ModelDir {
 };
 
 // Sequence slots over one PagePool, plus the device tables of a step: for token t of the packed batch its id, slot and
-// position, and for every wanted place its row in the batch. Filled on the host (pinned), uploaded with one copy.
+// position, and for every wanted place its row in the batch; for layers that carry state from token to token also the
+// position at which the token's sequence starts in this step and its length after it (what is older than the step comes
+// from carried state), and per entry its first batch row and its token count. Filled on the host (pinned), uploaded with
+// one copy.
 class SequenceBatch {
 public:
     ~SequenceBatch();
@@ -47,13 +51,44 @@ public:
     const int* d_slot() const { return dev_ + cap_; }
     const int* d_pos() const { return dev_ + 2 * (size_t)cap_; }
     const int* d_want_rows() const { return dev_ + 3 * (size_t)cap_; }
+    const int* d_start() const { return dev_ + 4 * (size_t)cap_; }     // per token: position of its entry's first token
+    const int* d_end() const { return dev_ + 5 * (size_t)cap_; }       // per token: its sequence's length after the step
+    const int* d_ent_row() const { return dev_ + 6 * (size_t)cap_; }   // per entry: first row in the batch
+    const int* d_ent_len() const { return dev_ + 7 * (size_t)cap_; }   // per entry: tokens
+    int n_entries = 0;
 
 private:
     int ensure_capacity(int tokens);
-    int* host_ = nullptr;   // pinned [4, cap]
+    static constexpr int kTables = 8;
+    int* host_ = nullptr;   // pinned [kTables, cap]
     int* dev_ = nullptr;
     int cap_ = 0;
     cudaEvent_t copied_ = nullptr;   // the upload out of host_ has run (host_ may be rewritten)
+};
+
+// State that a layer carries from token to token for each sequence slot (a recurrent state, the last inputs of a short
+// convolution): one fp32 block per slot, addressed by the slot index that SequenceBatch hands out. Nothing is cleared
+// when a slot changes owner: kernels start from zero whenever a sequence starts at position 0.
+class SlotState {
+public:
+    SlotState() = default;
+    SlotState(const SlotState&) = delete;
+    SlotState& operator=(const SlotState&) = delete;
+    SlotState(SlotState&& o) noexcept : dev_(o.dev_), per_slot_(o.per_slot_) { o.dev_ = nullptr; }
+    ~SlotState() { if (dev_) cudaFree(dev_); }
+    cudaError_t init(int n_slots, size_t floats_per_slot) {
+        per_slot_ = floats_per_slot;
+        const size_t bytes = std::max<size_t>(16, (size_t)n_slots * floats_per_slot * sizeof(float));
+        cudaError_t e = cudaMalloc(&dev_, bytes);
+        if (e == cudaSuccess) e = cudaMemset(dev_, 0, bytes);
+        return e;
+    }
+    float* data() const { return dev_; }
+    size_t floats_per_slot() const { return per_slot_; }
+
+private:
+    float* dev_ = nullptr;
+    size_t per_slot_ = 0;
 };
 
 class Model {

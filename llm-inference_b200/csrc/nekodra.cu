@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "launch_count.h"
 #include "model_registry.h"
+#include "checkpoint_upload.h"
 #include "safetensors.h"
 
 namespace b200 {
@@ -140,31 +141,7 @@ private:
 
 int Nekodra::upload(const SafeTensorsFile& st, const std::string& name, std::vector<long long> shape, bool as_f32, void* dst,
                     std::string& err) {
-    const SafeTensor* t = st.find(name);
-    if (!t) { err = "tensor " + name + " is missing"; return B200_EINVAL; }
-    if (t->shape != shape) {
-        std::string got, want;
-        for (long long d : t->shape) got += std::to_string(d) + ",";
-        for (long long d : shape) want += std::to_string(d) + ",";
-        err = "tensor " + name + " has shape [" + got + "], the configuration needs [" + want + "]";
-        return B200_EINVAL;
-    }
-    if (t->dtype != "BF16" && t->dtype != "F32") { err = "tensor " + name + ": dtype " + t->dtype + " not supported here"; return B200_EINVAL; }
-    const size_t n = t->elems();
-    cudaError_t e;
-    if (!as_f32 && dtype_ == B200_BF16 && t->dtype == "BF16") {
-        e = cudaMemcpy(dst, t->data, n * 2, cudaMemcpyHostToDevice);
-    } else if (!as_f32 && dtype_ == B200_BF16) {
-        std::vector<__nv_bfloat16> tmp(n);
-        for (size_t i = 0; i < n; ++i) tmp[i] = __float2bfloat16_rn(st_value(*t, i));
-        e = cudaMemcpy(dst, tmp.data(), n * 2, cudaMemcpyHostToDevice);
-    } else {
-        std::vector<float> tmp(n);
-        for (size_t i = 0; i < n; ++i) tmp[i] = st_value(*t, i);
-        e = cudaMemcpy(dst, tmp.data(), n * 4, cudaMemcpyHostToDevice);
-    }
-    if (e != cudaSuccess) { err = "upload of " + name + ": " + cudaGetErrorString(e); return (int)e; }
-    return B200_OK;
+    return upload_tensor(st, name, shape, as_f32, dtype_, dst, err);
 }
 
 #define NK_TRY(call)                    \

@@ -1,0 +1,142 @@
+// Between the q / k projection and the cache of an attention layer: rotary angles of a step (double-precision angle,
+// one table per frequency set), the short causal convolution over time with its carried inputs, the per-head RMS norm,
+// the rotation in either pairing, and the store of q, k (and of the convolved keys as values) — b200_qk_prepare — plus
+// the update of the convolution's ring of carried inputs. All arithmetic fp32; only the stores take the serving dtype.
+#include "b200_serve.h"
+#include "common.cuh"
+#include "launch_count.h"
+#include "rotary.cuh"
+
+namespace b200 {
+
+__global__ void rope_angles_kernel(const int* __restrict__ pos, const double* __restrict__ freq, int n_freq, int total,
+                                   float* __restrict__ cos_out, float* __restrict__ sin_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const double a = (double)pos[i / n_freq] * freq[i % n_freq];
+    double s, c;
+    sincos(a, &s, &c);
+    cos_out[i] = (float)c;
+    sin_out[i] = (float)s;
+}
+
+struct QkPrep {
+    const float* proj; long long ld_proj;
+    const float* conv_w; int taps; const float* conv_state;
+    const float* q_norm; const float* k_norm; float eps;
+    const float* cos; const float* sin; int rot_dims, rot_layout;
+    void* q_out; void* k_pool; void* v_pool; int v_from_conv;
+    const int* pages; int max_pages, page_rows;
+    const int* slot; const int* pos; const int* start;
+    int heads, kv_heads, dim;
+};
+
+// grid (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads. One thread per
+// dimension (strided when dim > blockDim).
+template <typename T>
+__global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrep a) {
+    extern __shared__ float vals[];   // [dim]: the normed head before rotation
+    __shared__ float red[4];
+    const int t = blockIdx.x, u = blockIdx.y, dim = a.dim;
+    const bool is_k = u >= a.heads;
+    const int ch0 = u * dim;          // first channel of this head in [q channels | k channels]
+    const int channels = (a.heads + a.kv_heads) * dim;
+    const int p = a.pos[t], b = a.slot[t];
+    size_t cache_row = 0;
+    if (is_k) cache_row = ((size_t)a.pages[(size_t)b * a.max_pages + p / a.page_rows] * a.page_rows + p % a.page_rows) * a.kv_heads + (u - a.heads);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+        const int c = ch0 + i;
+        float y;
+        if (a.conv_w) {
+            const int first = a.start[t], taps = a.taps;
+            y = 0.f;
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j, src = p - back;
+                if (src < 0) continue;
+                const float uin = src >= first ? a.proj[(size_t)(t - back) * a.ld_proj + c]
+                                               : a.conv_state[((size_t)b * (taps - 1) + src % (taps - 1)) * channels + c];
+                y = fmaf(a.conv_w[(size_t)c * taps + j], uin, y);
+            }
+        } else
+            y = a.proj[(size_t)t * a.ld_proj + c];
+        if (is_k && a.v_from_conv) reinterpret_cast<T*>(a.v_pool)[cache_row * dim + i] = DT<T>::from_f(y);
+        vals[i] = y;
+        ss += y * y;
+    }
+    const float* nw = is_k ? a.k_norm : a.q_norm;
+    float rinv = 1.f;
+    if (nw) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int k = 0; k < (int)blockDim.x / 32; ++k) tot += red[k];
+        rinv = 1.0f / sqrtf(tot / (float)dim + a.eps);
+        for (int i = threadIdx.x; i < dim; i += blockDim.x) vals[i] = vals[i] * rinv * nw[i];
+    }
+    __syncthreads();
+    const int nf = a.rot_dims / 2;
+    T* dst = is_k ? reinterpret_cast<T*>(a.k_pool) + cache_row * dim : reinterpret_cast<T*>(a.q_out) + ((size_t)t * a.heads + u) * dim;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        dst[i] = DT<T>::from_f(rotary_component(vals, i, a.rot_dims, a.rot_layout, a.cos + (size_t)t * nf, a.sin + (size_t)t * nf));
+}
+
+__global__ void conv_state_update_kernel(const float* __restrict__ proj, long long ld_proj, float* __restrict__ state,
+                                         const int* __restrict__ slot, const int* __restrict__ pos, const int* __restrict__ end,
+                                         int channels, int taps) {
+    const int t = blockIdx.x, p = pos[t];
+    if (p < end[t] - (taps - 1)) return;   // only the last taps-1 inputs of a sequence are carried
+    float* dst = state + ((size_t)slot[t] * (taps - 1) + p % (taps - 1)) * channels;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x) dst[c] = proj[(size_t)t * ld_proj + c];
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_rope_angles(const int* pos, int n_tokens, const double* freq, int n_freq, float* cos_out, float* sin_out,
+                                void* stream) {
+    if (!pos || !freq || !cos_out || !sin_out || n_tokens < 0 || n_freq < 0) return B200_EINVAL;
+    const int total = n_tokens * n_freq;
+    if (total == 0) return B200_OK;
+    rope_angles_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(pos, freq, n_freq, total, cos_out, sin_out);
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
+    if (!p || !p->proj || !p->q_out || !p->k_pool || !p->pages || !p->slot || !p->pos || p->n_tokens < 0 || p->heads < 1 ||
+        p->kv_heads < 1 || p->dim < 1 || p->page_rows < 1)
+        return B200_EINVAL;
+    if (p->conv_w && (p->taps < 1 || !p->start || (p->taps > 1 && !p->conv_state))) return B200_EINVAL;
+    if (p->v_from_conv && !p->v_pool) return B200_EINVAL;
+    if (p->rot_dims < 0 || (p->rot_dims & 1) || p->rot_dims > p->dim || (p->rot_dims && (!p->cos || !p->sin))) return B200_EINVAL;
+    if (p->rot_layout != B200_ROPE_HALF && p->rot_layout != B200_ROPE_INTERLEAVED) return B200_EINVAL;
+    if (p->n_tokens == 0) return B200_OK;
+    QkPrep a{p->proj, p->ld_proj, p->conv_w, p->taps, p->conv_state, p->q_norm, p->k_norm, p->eps, p->cos, p->sin, p->rot_dims,
+             p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
+             p->start, p->heads, p->kv_heads, p->dim};
+    if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
+    const dim3 grid(p->n_tokens, p->heads + p->kv_heads);
+    const int threads = p->dim <= 32 ? 32 : p->dim <= 64 ? 64 : 128;
+    const size_t smem = (size_t)p->dim * sizeof(float);
+    if (smem > 48 * 1024) return B200_EUNSUPPORTED;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (p->dtype == B200_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, threads, smem, s>>>(a);
+    else if (p->dtype == B200_F32) qk_prepare_kernel<float><<<grid, threads, smem, s>>>(a);
+    else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_conv_state_update(const float* proj, long long ld_proj, float* conv_state, const int* slot, const int* pos,
+                                      const int* end, int n_tokens, int channels, int taps, void* stream) {
+    if (!proj || !slot || !pos || !end || n_tokens < 0 || channels < 1 || taps < 1) return B200_EINVAL;
+    if (n_tokens == 0 || taps == 1) return B200_OK;
+    if (!conv_state) return B200_EINVAL;
+    conv_state_update_kernel<<<n_tokens, 128, 0, (cudaStream_t)stream>>>(proj, ld_proj, conv_state, slot, pos, end, channels, taps);
+    count_launch();
+    return (int)cudaGetLastError();
+}
