@@ -8,7 +8,8 @@ import numpy as np
 from . import capi
 
 F32, BF16 = 0, 2
-GG_NONE, GG_SIGMOID_MUL, GG_GLU = 0, 1, 2
+GG_NONE, GG_SIGMOID_MUL, GG_GLU, GG_GLU_GELU = 0, 1, 2, 3
+ROPE_HALF, ROPE_INTERLEAVED = 0, 1
 _vp, _i, _f, _sz, _ll = C.c_void_p, C.c_int, C.c_float, C.c_size_t, C.c_longlong
 
 
@@ -19,6 +20,31 @@ class GemmGroupedArgs(C.Structure):
                 ("stride_a", _ll), ("stride_w", _ll), ("stride_c", _ll), ("stride_aux", _ll),
                 ("M", _i), ("N", _i), ("K", _i), ("batch", _i), ("trans_b", _i), ("epi", _i),
                 ("a_dtype", _i), ("w_dtype", _i), ("c_dtype", _i)]
+
+
+class QkPrepareArgs(C.Structure):
+    """mirror of ``b200_qk_prepare_args``"""
+    _fields_ = [("proj", _vp), ("ld_proj", _ll), ("conv_w", _vp), ("taps", _i), ("conv_state", _vp),
+                ("q_norm", _vp), ("k_norm", _vp), ("eps", _f), ("cos", _vp), ("sin", _vp), ("rot_dims", _i), ("rot_layout", _i),
+                ("q_out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("v_from_conv", _i),
+                ("pages", _vp), ("max_pages", _i), ("page_rows", _i), ("slot", _vp), ("pos", _vp), ("start", _vp),
+                ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i)]
+
+
+class PagedAttentionArgs(C.Structure):
+    """mirror of ``b200_paged_attention_args``"""
+    _fields_ = [("q", _vp), ("out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("pages", _vp), ("max_pages", _i), ("page_rows", _i),
+                ("slot", _vp), ("pos", _vp), ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("vdim", _i),
+                ("scale", _f), ("softcap", _f), ("denom_bias", _f), ("dtype", _i), ("longest_entry", _i)]
+
+
+class RetentionArgs(C.Structure):
+    """mirror of ``b200_retention_args``"""
+    _fields_ = [("proj", _vp), ("ld_proj", _ll), ("q_off", _i), ("k_off", _i), ("v_off", _i),
+                ("cos", _vp), ("sin", _vp), ("rot_dims", _i), ("rot_layout", _i), ("decay", _vp), ("k_scale", _f),
+                ("state", _vp), ("out", _vp), ("ent_row", _vp), ("ent_len", _vp), ("slot", _vp), ("pos", _vp),
+                ("n_entries", _i), ("n_tokens", _i), ("heads", _i), ("dim", _i), ("vdim", _i), ("longest_entry", _i),
+                ("workspace", _vp), ("workspace_bytes", _sz)]
 
 
 class ModelOptions(C.Structure):
@@ -39,6 +65,16 @@ SERVE_PROTOTYPES = {
     "b200_moe_route": (_i, [_vp, _i, _vp, _vp, _i, _i, _i, _i, _f, _vp, _vp, _vp]),
     "b200_moe_dispatch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "b200_residual_combine": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "b200_layernorm_residual": (_i, [_vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "b200_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_softcap": (_i, [_vp, _sz, _f, _vp]),
+    "b200_rope_angles": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
+    "b200_qk_prepare": (_i, [C.POINTER(QkPrepareArgs), _vp]),
+    "b200_conv_state_update": (_i, [_vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_paged_attention": (_i, [C.POINTER(PagedAttentionArgs), _vp]),
+    "b200_retention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "b200_retention": (_i, [C.POINTER(RetentionArgs), _vp]),
+    "b200_unit_rms_gate": (_i, [_vp, _vp, _ll, _vp, _i, _i, _i, _f, _i, _vp]),
     "b200_serve_last_error": (C.c_char_p, []),
     "b200_model_families": (C.c_char_p, []),
     "b200_model_open": (_vp, [C.c_char_p, C.POINTER(ModelOptions)]),
@@ -234,4 +270,46 @@ def random_nekodra(width, heads, dim, vdim, kv_rank, experts, ff, top, identity,
         cfg["layers"].append(dict(type="latent_attention", mixer=mx,
                                   mlp=dict(kind="moe", expert=dict(ff=ff), shared=dict(ff=shared_ff),
                                            router=dict(experts=experts, identity=identity, top=top, scale=1.0))))
+    return cfg, w
+
+
+def random_musilorn(width, heads, kv_heads, dim, ff, n_layers, vocab, retention_every=0, ret_heads=0, ret_dim=0, ret_vdim=0,
+                    conv=4, loop=None, seed=0):
+    """(config, tensors) of a random Musilorn model: attention layers with a dense feed-forward; every
+    `retention_every`-th layer is a retention layer without one; `loop` = (start, stop, times) or None"""
+    import math
+
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16)
+
+    cfg = dict(architecture="Musilorn", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, logit_softcap=30.0, layers=[])
+    w = {"embed": rnd(vocab, width, s=1.0), "head": rnd(vocab, width), "final.norm": torch.ones(width), "final.norm.b": torch.zeros(width)}
+    if loop:
+        cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+        w["loop.in"] = rnd(width, 2 * width)
+    for i in range(n_layers):
+        pre = f"l{i}."
+        retention = retention_every > 0 and i % retention_every == retention_every - 1
+        for n in ("norm1", "norm1b") + (() if retention else ("norm2", "norm2b")):
+            w[pre + n], w[pre + n + ".b"] = torch.ones(width), torch.zeros(width)
+        if retention:
+            mx = dict(heads=ret_heads, dim=ret_dim, vdim=ret_vdim, rot=dict(base=10000.0, dims=ret_dim),
+                      decay=[1 - 2.0 ** (-5 - 5 * h / max(1, ret_heads - 1)) for h in range(ret_heads)])
+            w[pre + "mix.q"], w[pre + "mix.k"] = rnd(ret_heads * ret_dim, width), rnd(ret_heads * ret_dim, width)
+            w[pre + "mix.v"], w[pre + "mix.g"] = rnd(ret_heads * ret_vdim, width), rnd(ret_heads * ret_vdim, width)
+            w[pre + "mix.o"] = rnd(width, ret_heads * ret_vdim)
+            cfg["layers"].append(dict(type="retention", mixer=mx, mlp=None))
+            continue
+        mx = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, conv=conv, scale=1.0 / math.sqrt(dim), softcap=50.0,
+                  rot=dict(base=500000.0, dims=dim, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+        w[pre + "mix.q"], w[pre + "mix.k"] = rnd(heads * dim, width), rnd(kv_heads * dim, width)
+        w[pre + "mix.q.conv"], w[pre + "mix.k.conv"] = rnd(heads * dim, conv, s=0.5), rnd(kv_heads * dim, conv, s=0.5)
+        w[pre + "mix.q.norm"], w[pre + "mix.k.norm"] = torch.ones(dim), torch.ones(dim)
+        w[pre + "mix.o"] = rnd(width, heads * dim)
+        w[pre + "mlp.gate"], w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(ff, width), rnd(ff, width), rnd(width, ff)
+        cfg["layers"].append(dict(type="attention", mixer=mx, mlp=dict(kind="dense", ff=ff)))
     return cfg, w

@@ -191,3 +191,80 @@ class Oracle:
         for _ in range(n_new):
             ids.append(int(self.forward(ids)[-1].argmax()))
         return ids[len(prompt):]
+
+
+def random_model(seed, width=48, vocab=61, layers=None, loop=None, eps=1e-5, residual_mult=0.4, logit_softcap=12.0):
+    """A small random model of the design. `layers`: list of dicts, each with type ('attention' / 'retention'), the mixer's
+    sizes and 'ff' (or None for a layer without feed-forward). Returns (config, weights rounded to bfloat16 values)."""
+    g = torch.Generator().manual_seed(seed)
+
+    def rnd(*shape, s=None):
+        s = s if s is not None else 1.0 / math.sqrt(shape[-1])
+        return (torch.randn(*shape, generator=g) * s).bfloat16().float()
+
+    def norm(prefix, n):
+        w[prefix] = (1 + 0.2 * torch.randn(n, generator=g)).bfloat16().float()
+        w[prefix + ".b"] = rnd(n, s=0.1)
+
+    cfg = dict(architecture="Musilorn", vocab=vocab, width=width, norm=dict(eps=eps), residual_mult=residual_mult,
+               logit_softcap=logit_softcap, layers=[])
+    w = {"embed": rnd(vocab, width, s=1.0)}
+    if loop:
+        cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])
+        w["loop.in"] = rnd(width, 2 * width, s=1.0 / math.sqrt(width))
+    for i, L in enumerate(layers):
+        pre = f"l{i}."
+        norm(pre + "norm1", width)
+        norm(pre + "norm1b", width)
+        H, dim = L["heads"], L["dim"]
+        if L["type"] == "attention":
+            G, taps = L.get("kv_heads", H), L.get("conv", 4)
+            mx = dict(heads=H, kv_heads=G, dim=dim, vdim=dim, conv=taps, scale=L.get("scale", dim ** -0.5), softcap=L.get("softcap", 20.0),
+                      rot=dict(base=L.get("base", 10000.0), dims=L.get("rot_dims", dim)))
+            if L.get("scaling"):
+                mx["rot"]["scaling"] = L["scaling"]
+            w[pre + "mix.q"], w[pre + "mix.k"] = rnd(H * dim, width, s=2.0 / math.sqrt(width)), rnd(G * dim, width, s=2.0 / math.sqrt(width))
+            w[pre + "mix.q.conv"], w[pre + "mix.k.conv"] = rnd(H * dim, taps, s=0.6), rnd(G * dim, taps, s=0.6)
+            w[pre + "mix.q.norm"] = (1 + 0.3 * torch.randn(dim, generator=g)).bfloat16().float()
+            w[pre + "mix.k.norm"] = (1 + 0.3 * torch.randn(dim, generator=g)).bfloat16().float()
+            w[pre + "mix.o"] = rnd(width, H * dim)
+        else:
+            vdim = L["vdim"]
+            mx = dict(heads=H, dim=dim, vdim=vdim, decay=L["decay"], rot=dict(base=L.get("base", 10000.0), dims=L.get("rot_dims", dim)))
+            w[pre + "mix.q"], w[pre + "mix.k"] = rnd(H * dim, width), rnd(H * dim, width)
+            w[pre + "mix.v"], w[pre + "mix.g"] = rnd(H * vdim, width), rnd(H * vdim, width)
+            w[pre + "mix.o"] = rnd(width, H * vdim)
+        ml = None
+        if L.get("ff"):
+            ml = dict(kind="dense", ff=L["ff"])
+            norm(pre + "norm2", width)
+            norm(pre + "norm2b", width)
+            w[pre + "mlp.gate"], w[pre + "mlp.up"], w[pre + "mlp.down"] = rnd(L["ff"], width), rnd(L["ff"], width), rnd(width, L["ff"])
+        cfg["layers"].append(dict(type=L["type"], mixer=mx, mlp=ml))
+    norm("final.norm", width)
+    w["head"] = rnd(vocab, width)
+    return cfg, w
+
+
+def write_model(folder, cfg, weights):
+    """config.json + model.safetensors (bfloat16) in `folder`"""
+    import json
+    import os
+    import struct
+
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    header, blobs, off = {}, [], 0
+    for name, t in weights.items():
+        raw = t.bfloat16().contiguous().view(torch.int16).numpy().tobytes()
+        header[name] = dict(dtype="BF16", shape=list(t.shape), data_offsets=[off, off + len(raw)])
+        blobs.append(raw)
+        off += len(raw)
+    hj = json.dumps(header).encode()
+    hj += b" " * (-len(hj) % 8)
+    with open(os.path.join(folder, "model.safetensors"), "wb") as f:
+        f.write(struct.pack("<Q", len(hj)))
+        f.write(hj)
+        for b in blobs:
+            f.write(b)

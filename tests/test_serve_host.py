@@ -1,6 +1,7 @@
 """Host side of the model-family layer on a machine without a GPU: the registry, config.json / safetensors parsing
 and the error paths that end before any CUDA call."""
 import json
+import math
 import os
 
 import pytest
@@ -18,7 +19,7 @@ def S(pkg):
 
 def test_registry_lists_the_families(S):
     fams = S.lib().b200_model_families().decode().split(",")
-    assert "Nekodra" in fams
+    assert "Nekodra" in fams and "Musilorn" in fams and "llama" in fams
 
 
 def test_unknown_architecture_and_broken_config(S, tmp_path):
@@ -33,6 +34,45 @@ def test_unknown_architecture_and_broken_config(S, tmp_path):
     (tmp_path / "config.json").write_text('{"architecture": "Nekodra", "width": 8}')
     with pytest.raises(RuntimeError, match="required"):
         S.Model(tmp_path)
+
+
+def test_musilorn_configuration_errors_end_before_any_cuda_call(S, tmp_path):
+    (tmp_path / "config.json").write_text('{"architecture": "Musilorn", "width": 8, "vocab": 5, "norm": {"eps": 1e-5}, "layers": []}')
+    with pytest.raises(RuntimeError, match="required"):
+        S.Model(tmp_path)
+    (tmp_path / "config.json").write_text('{"architecture": "Musilorn", "width": 8, "vocab": 5, "norm": {"eps": 1e-5}, '
+                                          '"layers": [{"type": "attention", "mixer": {}, "mlp": null}]}')
+    with pytest.raises(RuntimeError, match="residual_mult"):
+        S.Model(tmp_path)
+
+
+def test_musilorn_oracle_pieces_agree_with_closed_forms():
+    """the plain implementation of the second family: rotation pairings, the convolution, the retention walk against its
+    unrolled sum, the softmax with one in the denominator, the order in which a repeated span runs"""
+    import musilorn_oracle as M
+    g = torch.Generator().manual_seed(1)
+    x = torch.randn(5, 2, 8, generator=g, dtype=torch.float64)
+    rot = dict(base=100.0, dims=4)
+    half, inter = M.rotate(x, rot, "half"), M.rotate(x, rot, "interleaved")
+    assert torch.equal(half[..., 4:], x[..., 4:]) and torch.equal(inter[0], x[0])          # beyond dims, and position 0
+    a = 3 * 100.0 ** (-2 / 4)                                                                # position 3, second frequency
+    assert torch.allclose(half[3, 0, 1], x[3, 0, 1] * math.cos(a) - x[3, 0, 3] * math.sin(a))
+    assert torch.allclose(inter[3, 0, 3], x[3, 0, 3] * math.cos(a) + x[3, 0, 2] * math.sin(a))
+    assert torch.allclose((half ** 2).sum(-1), (x ** 2).sum(-1))                            # a rotation keeps lengths
+    f = M.rot_frequencies(dict(base=10000.0, dims=8, scaling=dict(factor=4.0, low=1.0, high=4.0, original=128)))
+    plain = M.rot_frequencies(dict(base=10000.0, dims=8))
+    assert f[0] == plain[0] and torch.allclose(f[3], plain[3] / 4) and plain[1] / 4 < f[1] < plain[1]
+    u, w = torch.randn(6, 3, generator=g, dtype=torch.float64), torch.randn(3, 4, generator=g, dtype=torch.float64)
+    y = M.short_conv(u, w)
+    assert torch.allclose(y[0], w[:, 3] * u[0]) and torch.allclose(y[5], (w.T * u[2:6]).sum(0))
+    q, k, v = (torch.randn(7, n, generator=g, dtype=torch.float64) for n in (4, 4, 5))
+    o = M.retention_state_walk(q, k, v, 0.8)
+    assert torch.allclose(o[6], sum(0.8 ** (6 - j) * (q[6] @ k[j]) * v[j] for j in range(7)))
+    att = M.capped_sink_attention(q, k, v, 0.7, 2.0)
+    s = 2.0 * torch.tanh(k[:3] @ q[2] * 0.7 / 2.0)
+    assert torch.allclose(att[2], (torch.exp(s) / (1 + torch.exp(s).sum())) @ v[:3])
+    cfg = dict(layers=[0, 1, 2, 3], loop=dict(start=1, stop=3, times=2))
+    assert M.layer_runs(cfg) == [(0, False), (1, True), (2, False), (1, True), (2, False), (3, False)]
 
 
 def test_oracle_pieces_agree_with_torch():
