@@ -11,8 +11,8 @@ Workloads (BASELINE.json configs):
   cfg5: LLaMA-2-70B-shaped GQA (64 q / 8 kv heads, 80 layers) fp16 decode, tensor parallel over the N GPUs
         (strong scaling: heads / FFN columns split, allreduce after o_proj and down_proj only);
         --comm p2p = the fused one-shot NVLink allreduce + residual kernel, --comm nccl = the NCCL baseline.
-  nekodra: not a BASELINE.json config: prefill and decode tokens/s of the Nekodra family (include/b200_serve.h, random
-        weights, --size s|m) beside the LLaMA engine at equal size; prints a line of its own shape.
+  nekodra, musilorn: not BASELINE.json configs: prefill and decode tokens/s of the Nekodra / Musilorn family
+        (include/b200_serve.h, random weights, --size s|m) beside the LLaMA engine at equal size; a line of its own shape.
   cfg3: prefill, batch 4 x 2048 prompt tokens per GPU (metric prefill_tokens_per_s; a step = one prompt
         pass of the whole model: tcgen05 GEMMs + flash context attention; roofline = tensor).
 `value`  : tokens/s with everything resident in HBM, CUDA events on the engine's stream, max over ranks.
@@ -46,9 +46,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "nekodra"])
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg3", "cfg4", "cfg5", "nekodra", "musilorn"])
     ap.add_argument("--size", default="m", choices=["s", "m"],
-                    help="nekodra: model shape (llm-inference_b200/bench_families.py SIZES)")
+                    help="nekodra / musilorn: model shape (llm-inference_b200/bench_families.py SIZES, MUSILORN_SIZES)")
     ap.add_argument("--prompt", type=int, default=2048, help="nekodra: prompt tokens of the prefill measurement")
     ap.add_argument("--comm", default="p2p", choices=["p2p", "nccl"],
                     help="cfg5: fused one-shot NVLink allreduce (product) or ncclAllReduce + AddResidual (baseline)")
@@ -904,20 +904,20 @@ def extras_multi_gpu(pkg, args, rank, world, local_rank, peak):
 # the B200 arm
 # --------------------------------------------------------------------------------------------
 def bench_family(args):
-    """--workload nekodra: prefill and decode tokens/s of the Nekodra family (include/b200_serve.h) beside the LLaMA engine
+    """--workload nekodra | musilorn: prefill and decode tokens/s of that family (include/b200_serve.h) beside the LLaMA engine
     at equal size; one JSON line of its own shape (the default workload's line and contract are untouched)."""
     from __graft_entry__ import load_package
     pkg = load_package()
     from llm_inference_b200 import bench_families
     res = bench_families.run(pkg, size=args.size, prompt=args.prompt, batch=args.batch or 8, context=args.context or 1024,
-                             steps=min(args.steps, 20), warmup=max(args.warmup, 3))
+                             steps=min(args.steps, 20), warmup=max(args.warmup, 3), family=args.workload)
     res["gpu_launches"] = int(pkg.capi.lib().b200_launch_count())
     print(json.dumps(res))
 
 
 def main():
     args = parse()
-    if args.workload == "nekodra":
+    if args.workload in ("nekodra", "musilorn"):
         return bench_family(args)
     wl = workload(args)
     rank = int(os.environ.get("RANK", "0"))

@@ -156,7 +156,8 @@ int b200_conv_state_update(const float* proj, long long ld_proj, float* conv_sta
  * a value; 0: plain softmax); out[t, h, :] = sum_j p_j v_j. q [n_tokens, heads*dim], out [n_tokens, heads*vdim], pools
  * [n_pages*page_rows, kv_heads, dim | vdim], all of `dtype`; scores, softmax and sums in fp32.
  * longest_entry (0 = unknown): most tokens one sequence brings in this batch; bfloat16 batches with prompt portions run
- * on tensor-core tiles, single tokens and fp32 on the row kernel. */
+ * on tensor-core tiles, single tokens and fp32 on the row kernel; with a workspace and longest_context given, a batch of few
+ * rows with long contexts (decoding) splits every context over up to 16 CTAs and merges the shares in a second launch. */
 typedef struct b200_paged_attention_args {
     const void* q; void* out; const void* k_pool; const void* v_pool;
     const int* pages; int max_pages, page_rows;
@@ -164,7 +165,10 @@ typedef struct b200_paged_attention_args {
     int n_tokens, heads, kv_heads, dim, vdim;
     float scale, softcap, denom_bias;
     int dtype, longest_entry;
+    int longest_context;                       /* most rows any token sees (0 = unknown)                          */
+    void* workspace; size_t workspace_bytes;   /* shares of split contexts (may be NULL: no splitting)            */
 } b200_paged_attention_args;
+size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, int vdim);
 int b200_paged_attention(const b200_paged_attention_args* a, void* stream);
 
 /* Retention: linear attention with a fixed decay per head and a carried state, no softmax. For every entry (a run of

@@ -1,6 +1,6 @@
 """Prefill and decode throughput of a model family served through include/b200_serve.h, beside the LLaMA engine at
 equal size (same width, heads, layers, vocabulary and the same feed-forward width per token), random weights.
-Called by bench.py --workload nekodra; prints one JSON line."""
+Called by bench.py --workload nekodra | musilorn; prints one JSON line."""
 import json
 import os
 import tempfile
@@ -12,6 +12,15 @@ SIZES = {
               n_layers=4, vocab=32000),
     "m": dict(width=2048, heads=16, dim=128, vdim=128, kv_rank=512, experts=16, ff=1024, top=4, identity=2, shared_ff=2048,
               n_layers=4, vocab=32000),
+}
+
+
+MUSILORN_SIZES = {
+    # attention layers with a dense feed-forward; the last layer is a retention layer without one
+    "s": dict(width=1024, heads=8, kv_heads=4, dim=128, ff=4096, n_layers=4, vocab=32000, retention_every=4, ret_heads=4, ret_dim=128,
+              ret_vdim=256),
+    "m": dict(width=2048, heads=16, kv_heads=8, dim=128, ff=8192, n_layers=4, vocab=32000, retention_every=4, ret_heads=8, ret_dim=128,
+              ret_vdim=256),
 }
 
 
@@ -27,18 +36,21 @@ def timed(fn, steps, warmup):
     return (time.perf_counter() - t0) / steps
 
 
-def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, dtype="bfloat16"):
+def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, dtype="bfloat16", family="nekodra"):
     import numpy as np
     import torch
 
     S, E, capi = pkg.serve, pkg.engine, pkg.capi
-    sz = SIZES[size]
+    sz = (MUSILORN_SIZES if family == "musilorn" else SIZES)[size]
     rng = np.random.default_rng(0)
-    out = {"workload": "nekodra", "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
+    out = {"workload": family, "size": size, "shape": sz, "prompt": prompt, "decode_batch": batch, "decode_context": context,
            "dtype": dtype, "data": "synthetic ids, random weights", "timing": "host clock around synchronous steps (each step ends "
            "with the device-to-host copy of its results), after warm-up"}
     with tempfile.TemporaryDirectory() as folder:
-        cfg, w = S.random_nekodra(max_positions=max(prompt, context + steps + warmup + 8) + 64, **sz)
+        if family == "musilorn":
+            cfg, w = S.random_musilorn(**sz)
+        else:
+            cfg, w = S.random_nekodra(max_positions=max(prompt, context + steps + warmup + 8) + 64, **sz)
         S.write_checkpoint(folder, cfg, w)
         del w
         PR = 64
@@ -64,9 +76,10 @@ def run(pkg, size="m", prompt=2048, batch=8, context=1024, steps=10, warmup=3, d
 
     # the closest existing model: the LLaMA engine with the same width, heads, layers and vocabulary, and the
     # feed-forward width a Nekodra token actually uses (its chosen experts + the shared one); fp16
-    inter = sz["top"] * sz["ff"] + sz["shared_ff"]
-    shape = dict(num_layers=sz["n_layers"], head_num=sz["heads"], kv_head_num=sz["heads"], head_size=sz["dim"], inter_size=inter,
-                 vocab_size=V)
+    # (Musilorn: the same grouped heads and feed-forward width; its retention layer stands against one more attention layer)
+    inter = sz["ff"] if family == "musilorn" else sz["top"] * sz["ff"] + sz["shared_ff"]
+    shape = dict(num_layers=sz["n_layers"], head_num=sz["heads"], kv_head_num=sz.get("kv_heads", sz["heads"]), head_size=sz["dim"],
+                 inter_size=inter, vocab_size=V)
     ll = {"shape": shape, "dtype": "fp16"}
     try:
         eng = E.Engine(1, prompt + 8, dtype=capi.F16, **shape)

@@ -10,6 +10,9 @@
 //   paged_attn_tile_kernel  bfloat16 prompt portions on mma.sync tiles (further down).
 #include <cuda_bf16.h>
 #include <math.h>
+#include <stdlib.h>
+
+#include <algorithm>
 
 #include "b200_serve.h"
 #include "common.cuh"
@@ -23,9 +26,11 @@ struct PA {
     const int* slot; const int* pos;
     int n_tokens, heads, kv_heads, dim, vdim;
     float scale, softcap, denom_bias;
+    int splits; float* part;   // row kernel: shares of a context split over gridDim.z CTAs, [token, head, split, 2 + vdim]
 };
 
 constexpr int kRowWarps = 4;
+constexpr int kMaxSplits = 16;
 constexpr int kMaxVPerLane = 8;   // vdim <= 256
 
 template <typename T>
@@ -72,10 +77,13 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     float m = -INFINITY, l = 0.f, o[kMaxVPerLane];
 #pragma unroll
     for (int c = 0; c < kMaxVPerLane; ++c) o[c] = 0.f;
-    if (warp == 0 && a.denom_bias > 0.f) { m = 0.f; l = a.denom_bias; }
-    for (int j0 = warp * 32; j0 <= p; j0 += kRowWarps * 32) {
+    // this CTA's share of the keys: whole blocks of 32, the sink with the first share
+    const int per = ((p + a.splits) / a.splits + 31) & ~31;
+    const int j_begin = blockIdx.z * per, j_end = min(p + 1, j_begin + per);
+    if (warp == 0 && blockIdx.z == 0 && a.denom_bias > 0.f) { m = 0.f; l = a.denom_bias; }
+    for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
         const int j = j0 + lane;
-        const bool ok = j <= p;
+        const bool ok = j < j_end;
         size_t row = 0;
         float s = -INFINITY;
         if (ok) {
@@ -96,7 +104,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
         m = mn;
 #pragma unroll
         for (int c = 0; c < kMaxVPerLane; ++c) o[c] *= corr;
-        const int n = min(32, p - j0 + 1);
+        const int n = min(32, j_end - j0);
         for (int kk = 0; kk < n; ++kk) {
             const float pk = __shfl_sync(0xffffffffu, pj, kk);
             const size_t r = __shfl_sync(0xffffffffu, (unsigned long long)row, kk);
@@ -114,7 +122,17 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     float M = ms[0];
     for (int w = 1; w < kRowWarps; ++w) M = fmaxf(M, ms[w]);
     float L = 0.f;
-    for (int w = 0; w < kRowWarps; ++w) L += ls[w] * expf(ms[w] - M);
+    for (int w = 0; w < kRowWarps; ++w) L += M == -INFINITY ? 0.f : ls[w] * expf(ms[w] - M);
+    if (a.splits > 1) {   // an unnormalised share: (m, l, o); an empty share is (-inf, 0, 0)
+        float* pr = a.part + (((size_t)t * a.heads + h) * a.splits + blockIdx.z) * (a.vdim + 2);
+        if (threadIdx.x == 0) { pr[0] = M; pr[1] = L; }
+        for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
+            float v = 0.f;
+            for (int w = 0; w < kRowWarps; ++w) v += M == -INFINITY ? 0.f : om[w * a.vdim + c] * expf(ms[w] - M);
+            pr[2 + c] = v;
+        }
+        return;
+    }
     T* dst = reinterpret_cast<T*>(a.out) + ((size_t)t * a.heads + h) * a.vdim;
     for (int c = threadIdx.x; c < a.vdim; c += blockDim.x) {
         float v = 0.f;
@@ -123,9 +141,228 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     }
 }
 
+// merges the shares of split contexts: one CTA per (token, head)
+template <typename T>
+__global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int splits, int vdim) {
+    const float* pr = part + (size_t)blockIdx.x * splits * (vdim + 2);
+    float M = -INFINITY;
+    for (int z = 0; z < splits; ++z) M = fmaxf(M, pr[(size_t)z * (vdim + 2)]);
+    float L = 0.f, wz[kMaxSplits];
+    for (int z = 0; z < splits; ++z) {
+        const float mz = pr[(size_t)z * (vdim + 2)];
+        wz[z] = mz == -INFINITY ? 0.f : expf(mz - M);
+        L += pr[(size_t)z * (vdim + 2) + 1] * wz[z];
+    }
+    for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+        float v = 0.f;
+        for (int z = 0; z < splits; ++z) v += pr[(size_t)z * (vdim + 2) + 2 + c] * wz[z];
+        out[(size_t)blockIdx.x * vdim + c] = DT<T>::from_f(v / L);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// bfloat16 prompt portions on tensor-core tiles (mma.sync m16n8k16, fp32 accumulation): a CTA of four warps owns 64
+// consecutive rows of the packed batch for one query head; each warp keeps its 16 rows' Q fragments and output
+// accumulators in registers and walks the keys in tiles of 64 that land in shared memory by cp.async (two buffers, the
+// next tile in flight while this one is multiplied). Scores, cap, mask and the online softmax stay in fp32 registers;
+// the probabilities are rounded to bfloat16 only as the operand of the second product. Rows of the tile that belong
+// to different sequences are handled segment by segment (the other rows masked), so prompt portions, single tokens and
+// mixed batches share the launch. The sink is the initial state of every row (m = 0, l = denom_bias).
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kTileM = 64, kTileN = 64;
+
+__device__ __forceinline__ void pa_ldsm_x4(uint32_t (&r)[4], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void pa_ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+}
+__device__ __forceinline__ void pa_mma(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ uint32_t pa_pack(float lo, float hi) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
+template <int D>   // dim == vdim == D
+__global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
+    using bf = __nv_bfloat16;
+    constexpr int RS = D + 8;                 // row stride in elements: 16-byte aligned, conflict-free fragment loads
+    constexpr int CH = D / 8;                 // 16-byte chunks per row
+    extern __shared__ __align__(16) unsigned char pa_smem[];
+    bf* Qs = reinterpret_cast<bf*>(pa_smem);                  // [64][RS]
+    bf* Ks = Qs + kTileM * RS;                                // [2][64][RS]
+    bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RS]
+    int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RS);   // [64], -1: no such row
+    int* row_slot = row_pos + kTileM;
+    const int t0 = blockIdx.x * kTileM, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gid = lane >> 2, tig = lane & 3;
+    const int rows = min(kTileM, a.n_tokens - t0);
+    for (int r = threadIdx.x; r < kTileM; r += blockDim.x) {
+        row_pos[r] = r < rows ? a.pos[t0 + r] : -1;
+        row_slot[r] = r < rows ? a.slot[t0 + r] : -1;
+    }
+    const bf* Q = reinterpret_cast<const bf*>(a.q);
+    for (int i = threadIdx.x; i < kTileM * CH; i += blockDim.x) {
+        const int r = i / CH, c = i % CH;
+        Pack16 v{{0u, 0u, 0u, 0u}};
+        if (r < rows) v = ld16(Q + ((size_t)(t0 + r) * a.heads + h) * D + c * 8);
+        st16(Qs + r * RS + c * 8, v);
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        pa_ldsm_x4(qf[ks], Qs + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + ks * 16 + (lane >> 4) * 8);
+    float o[D / 8][4];
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    const float m0 = a.denom_bias > 0.f ? 0.f : -1e30f;
+    float m_run[2] = {m0, m0}, l_run[2] = {a.denom_bias, a.denom_bias};
+    const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;
+    const bf* Kp = reinterpret_cast<const bf*>(a.k_pool);
+    const bf* Vp = reinterpret_cast<const bf*>(a.v_pool);
+
+    for (int seg = 0; seg < rows;) {
+        const int b = row_slot[seg];
+        int seg_end = seg + 1;
+        while (seg_end < rows && row_slot[seg_end] == b) ++seg_end;
+        const int n_keys = row_pos[seg_end - 1] + 1;            // positions grow along an entry
+        const int* plist = a.pages + (size_t)b * a.max_pages;
+        // this thread's two rows in this segment, and the last key any row of the warp sees
+        const int p_lo = (r_lo >= seg && r_lo < seg_end) ? row_pos[r_lo] : -1;
+        const int p_hi = (r_hi >= seg && r_hi < seg_end) ? row_pos[r_hi] : -1;
+        const int w_first = max(seg, warp * 16), w_last = min(seg_end, warp * 16 + 16) - 1;
+        const int warp_keys = w_last >= w_first ? row_pos[w_last] + 1 : 0;
+        auto load_tile = [&](int k0, int buf) {
+            bf* kd = Ks + buf * kTileN * RS;
+            bf* vd = Vs + buf * kTileN * RS;
+            for (int i = threadIdx.x; i < kTileN * CH; i += blockDim.x) {
+                const int kr = i / CH, c = i % CH, j = k0 + kr;
+                const bool ok = j < n_keys;
+                const size_t row = ok ? ((size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows) * a.kv_heads + g : 0;
+                const uint32_t bytes = ok ? 16u : 0u;                 // beyond the sequence: zeros, nothing is read
+                const uint32_t kdst = (uint32_t)__cvta_generic_to_shared(kd + kr * RS + c * 8);
+                const uint32_t vdst = (uint32_t)__cvta_generic_to_shared(vd + kr * RS + c * 8);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(kdst), "l"(Kp + row * D + c * 8), "r"(bytes) : "memory");
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(vdst), "l"(Vp + row * D + c * 8), "r"(bytes) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        __syncthreads();   // the buffers of the previous segment are no longer read
+        load_tile(0, 0);
+        int buf = 0;
+        for (int k0 = 0; k0 < n_keys; k0 += kTileN, buf ^= 1) {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();   // tile k0 has landed for everybody; the other buffer is no longer read
+            if (k0 + kTileN < n_keys) load_tile(k0 + kTileN, buf ^ 1);
+            if (k0 >= warp_keys) continue;   // causal: nothing for this warp's rows from here on (it keeps the barriers)
+            const bf* Kb = Ks + buf * kTileN * RS;
+            const bf* Vb = Vs + buf * kTileN * RS;
+            float s[kTileN / 8][4];
+#pragma unroll
+            for (int nt = 0; nt < kTileN / 8; ++nt) {
+                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+                const bf* krow = Kb + (nt * 8 + gid) * RS + tig * 2;
+#pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    uint32_t bfr[2];
+                    bfr[0] = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
+                    bfr[1] = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
+                    pa_mma(s[nt], qf[ks], bfr);
+                }
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = k0 + nt * 8 + tig * 2 + (e & 1);
+                    float v = s[nt][e] * a.scale;
+                    if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                    v = j <= ((e & 2) ? p_hi : p_lo) ? v : -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float alpha[2];
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 1));
+                mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 2));
+                const float mn = fmaxf(m_run[hrow], mx[hrow]);   // finite: m starts at 0 (the sink) or at -1e30
+                alpha[hrow] = expf(m_run[hrow] - mn);
+                m_run[hrow] = mn;
+            }
+            float sum[2] = {0.f, 0.f};
+#pragma unroll
+            for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = expf(s[nt][e] - m_run[e >> 1]);   // masked: exp(-inf) = 0
+                    s[nt][e] = pv;
+                    sum[e >> 1] += pv;
+                }
+#pragma unroll
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                sum[hrow] += __shfl_xor_sync(0xffffffffu, sum[hrow], 1);
+                sum[hrow] += __shfl_xor_sync(0xffffffffu, sum[hrow], 2);
+                l_run[hrow] = l_run[hrow] * alpha[hrow] + sum[hrow];
+            }
+#pragma unroll
+            for (int nt = 0; nt < D / 8; ++nt) { o[nt][0] *= alpha[0]; o[nt][1] *= alpha[0]; o[nt][2] *= alpha[1]; o[nt][3] *= alpha[1]; }
+#pragma unroll
+            for (int kk = 0; kk < kTileN / 16; ++kk) {
+                uint32_t pf[4];
+                pf[0] = pa_pack(s[2 * kk][0], s[2 * kk][1]);
+                pf[1] = pa_pack(s[2 * kk][2], s[2 * kk][3]);
+                pf[2] = pa_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+                pf[3] = pa_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+                for (int nt = 0; nt < D / 8; ++nt) {
+                    uint32_t bfr[2];
+                    pa_ldsm_x2_trans(bfr, Vb + (kk * 16 + (lane & 15)) * RS + nt * 8);
+                    pa_mma(o[nt], pf, bfr);
+                }
+            }
+        }
+        seg = seg_end;
+    }
+    bf* out = reinterpret_cast<bf*>(a.out);
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+        const int r = hrow ? r_hi : r_lo;
+        if (r >= rows) continue;
+        const float inv = 1.0f / l_run[hrow];
+        bf* dst = out + ((size_t)(t0 + r) * a.heads + h) * D + tig * 2;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt)
+            *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) = __floats2bfloat162_rn(o[nt][hrow * 2] * inv, o[nt][hrow * 2 + 1] * inv);
+    }
+}
+
+template <int D>
+static int launch_tile(const PA& a, cudaStream_t s) {
+    constexpr int smem = (kTileM + 4 * kTileN) * (D + 8) * 2 + 2 * kTileM * 4;
+    static unsigned long long done = 0;
+    const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D>, smem, done);
+    if (e != cudaSuccess) return (int)e;
+    paged_attn_tile_kernel<D><<<dim3((a.n_tokens + kTileM - 1) / kTileM, a.heads), 128, smem, s>>>(a);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" size_t b200_paged_attention_workspace_bytes(int n_tokens, int heads, int vdim) {
+    if (n_tokens < 1 || heads < 1 || vdim < 1 || (long long)n_tokens * heads >= 2 * sm_count()) return 0;
+    return (size_t)n_tokens * heads * kMaxSplits * (vdim + 2) * sizeof(float);
+}
 
 extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* stream) {
     if (!p || !p->q || !p->out || !p->k_pool || !p->v_pool || !p->pages || !p->slot || !p->pos || p->n_tokens < 0 || p->heads < 1 ||
@@ -134,14 +371,36 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
     if (p->vdim > 32 * kMaxVPerLane) return B200_EUNSUPPORTED;
     if (p->n_tokens == 0) return B200_OK;
     PA a{p->q, p->out, p->k_pool, p->v_pool, p->pages, p->max_pages, p->page_rows, p->slot, p->pos, p->n_tokens, p->heads,
-         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias};
+         p->kv_heads, p->dim, p->vdim, p->scale, p->softcap, p->denom_bias, 1, nullptr};
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(p->n_tokens, p->heads);
     const size_t smem = ((size_t)p->dim + (size_t)kRowWarps * p->vdim) * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
-    if (p->dtype == B200_BF16) paged_attn_row_kernel<__nv_bfloat16><<<grid, kRowWarps * 32, smem, s>>>(a);
-    else if (p->dtype == B200_F32) paged_attn_row_kernel<float><<<grid, kRowWarps * 32, smem, s>>>(a);
+    auto al16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) == 0; };
+    const char* env = getenv("B200_ATTN_ROWS");   // 1: every batch on the row kernel (debugging aid)
+    if (p->dtype == B200_BF16 && p->longest_entry != 1 && p->dim == p->vdim && (p->dim == 64 || p->dim == 128 || p->dim == 32) &&
+        al16(p->q) && al16(p->out) && al16(p->k_pool) && al16(p->v_pool) && !(env && env[0] == '1')) {
+        const int rc = p->dim == 128 ? launch_tile<128>(a, s) : p->dim == 64 ? launch_tile<64>(a, s) : launch_tile<32>(a, s);
+        if (rc == 0) count_launch();
+        return rc;
+    }
+    // few rows with long contexts (decode batches): split every context over several CTAs and merge the shares
+    if (p->longest_context > 256 && p->workspace && (long long)p->n_tokens * p->heads < 2 * sm_count()) {
+        int splits = (int)((4ll * sm_count() + (long long)p->n_tokens * p->heads - 1) / ((long long)p->n_tokens * p->heads));
+        splits = std::min(std::min(splits, kMaxSplits), (p->longest_context + 127) / 128);
+        if (splits > 1 && p->workspace_bytes >= (size_t)p->n_tokens * p->heads * splits * (p->vdim + 2) * sizeof(float)) {
+            a.splits = splits;
+            a.part = reinterpret_cast<float*>(p->workspace);
+        }
+    }
+    const dim3 grid3(p->n_tokens, p->heads, a.splits);
+    if (p->dtype == B200_BF16) paged_attn_row_kernel<__nv_bfloat16><<<grid3, kRowWarps * 32, smem, s>>>(a);
+    else if (p->dtype == B200_F32) paged_attn_row_kernel<float><<<grid3, kRowWarps * 32, smem, s>>>(a);
     else return B200_EINVAL;
     count_launch();
+    if (a.splits > 1) {
+        if (p->dtype == B200_BF16) paged_attn_combine_kernel<__nv_bfloat16><<<p->n_tokens * p->heads, 128, 0, s>>>(a.part, (__nv_bfloat16*)p->out, a.splits, p->vdim);
+        else paged_attn_combine_kernel<float><<<p->n_tokens * p->heads, 128, 0, s>>>(a.part, (float*)p->out, a.splits, p->vdim);
+        count_launch();
+    }
     return (int)cudaGetLastError();
 }

@@ -131,11 +131,11 @@ extern "C" int b200_layernorm_residual(float* x, const float* y, int n_rows, int
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == B200_BF16) {
         static unsigned long long done = 0;
-        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<__nv_bfloat16>, (int)smem, done);
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<__nv_bfloat16>, 200 * 1024, done);
         layernorm_residual_kernel<__nv_bfloat16><<<n_rows, 256, smem, s>>>(x, y, width, eps, mult, w, b, w2, b2, (__nv_bfloat16*)out2);
     } else if (out_dtype == B200_F32) {
         static unsigned long long done = 0;
-        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<float>, (int)smem, done);
+        if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<float>, 200 * 1024, done);
         layernorm_residual_kernel<float><<<n_rows, 256, smem, s>>>(x, y, width, eps, mult, w, b, w2, b2, (float*)out2);
     } else
         return B200_EINVAL;

@@ -72,6 +72,7 @@ public:
         for (void* p : owned_) cudaFree(p);
         cudaFree(scratch_);
         cudaFree(ws_);
+        cudaFree(attn_ws_);
         cudaFree(capture_);
         if (logits_host_) cudaFreeHost(logits_host_);
         if (stream_) cudaStreamDestroy(stream_);
@@ -137,6 +138,8 @@ private:
     char* scratch_ = nullptr;
     void* ws_ = nullptr;   // split-K partials of the weight-streaming GEMM
     size_t ws_bytes_ = 0;
+    void* attn_ws_ = nullptr;   // shares of split attention contexts / chunk states of retention
+    size_t attn_ws_bytes_ = 0;
     int cap_T_ = 0, cap_W_ = 0;
     float *x_ = nullptr, *x0_ = nullptr, *proj_ = nullptr, *y_ = nullptr, *ret_ = nullptr, *logits_ = nullptr, *cs_ = nullptr;
     void *h1_ = nullptr, *h2_ = nullptr, *cat_ = nullptr, *q_ = nullptr, *att_ = nullptr, *act_ = nullptr, *hf_ = nullptr;
@@ -439,8 +442,24 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
     MU_TRY(seq_.begin_step(entries, stream_, err));
     const int T = seq_.n_tokens, W = seq_.n_want, D = D_, dt = dtype_;
     if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
-    int longest_entry = 0;
-    for (const StepEntry& en : entries) longest_entry = std::max(longest_entry, en.n_tokens);
+    int longest_entry = 0, longest_context = 0;
+    for (const StepEntry& en : entries) {
+        longest_entry = std::max(longest_entry, en.n_tokens);
+        longest_context = std::max(longest_context, seq_.length[en.slot]);
+    }
+    {   // room for the shares of split contexts (batches of few rows) and for the chunk states of long retention entries
+        size_t need = 0;
+        for (const MuLayer& L : layers_)
+            need = std::max(need, L.attention ? b200_paged_attention_workspace_bytes(T, L.heads, L.vdim)
+                                              : b200_retention_workspace_bytes(T, seq_.n_entries, L.heads, L.dim, L.vdim));
+        if (need > attn_ws_bytes_) {
+            cudaStreamSynchronize(stream_);
+            cudaFree(attn_ws_);
+            attn_ws_ = nullptr;
+            attn_ws_bytes_ = 0;
+            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
+        }
+    }
     const int* pages = seq_.pool.device();
     const int max_pages = seq_.pool.max_pages();
     if (capture_on_) {
@@ -499,7 +518,8 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
             pa.slot = seq_.d_slot(); pa.pos = seq_.d_pos();
             pa.n_tokens = T; pa.heads = H; pa.kv_heads = L.kv_heads; pa.dim = L.dim; pa.vdim = L.vdim;
             pa.scale = L.scale; pa.softcap = L.softcap; pa.denom_bias = 1.f;
-            pa.dtype = dt; pa.longest_entry = longest_entry;
+            pa.dtype = dt; pa.longest_entry = longest_entry; pa.longest_context = longest_context;
+            pa.workspace = attn_ws_; pa.workspace_bytes = attn_ws_bytes_;
             MU_OP(b200_paged_attention(&pa, stream_));
         } else {
             b200_retention_args ra{};
@@ -512,6 +532,7 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
             ra.ent_row = seq_.d_ent_row(); ra.ent_len = seq_.d_ent_len(); ra.slot = seq_.d_slot(); ra.pos = seq_.d_pos();
             ra.n_entries = seq_.n_entries; ra.n_tokens = T; ra.heads = H; ra.dim = L.dim; ra.vdim = L.vdim;
             ra.longest_entry = longest_entry;
+            ra.workspace = attn_ws_; ra.workspace_bytes = attn_ws_bytes_;
             MU_OP(b200_retention(&ra, stream_));
             MU_OP(b200_unit_rms_gate(ret_, proj_ + 2 * H * L.dim + natt, L.n_in, att_, T, H, L.vdim, eps_, dt, stream_));
         }

@@ -5,8 +5,15 @@
 //                           S[:, c] in registers and walks the entry's tokens in order, S <- decay S + k_t v_t[c],
 //                           out[t, c] = <S[:, c], q_t>. Columns are independent, so no thread waits on another inside a
 //                           token; q_t and k_t are rotated and staged in shared memory eight tokens at a time.
-//                           Decode batches (one token per entry) and prompt portions take the same path.
+//                           Decode batches and short portions take this path.
+//   chunk form (entries of 128 tokens and more): the same recurrence regrouped over chunks of 64 tokens, three launches:
+//     retention_chunk_state_kernel   U_c = sum_j decay^(L-1-j) k_j v_j^T of every chunk, chunks in parallel;
+//     retention_chunk_scan_kernel    S at the start of every chunk, S_(c+1) = decay^L S_c + U_c, element-wise, and the
+//                                    state the entry leaves behind;
+//     retention_chunk_out_kernel     out_i = decay^(i+1) S_c^T q_i + sum_(j<=i) decay^(i-j) (q_i . k_j) v_j, chunks in parallel.
+//   The same sums in another order: results agree with the walk to fp32 rounding.
 #include <math.h>
+#include <stdlib.h>
 
 #include "b200_serve.h"
 #include "common.cuh"
@@ -81,6 +88,138 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const RT a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// chunk form
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kChunk = 64, kChunkCols = 64;
+
+struct RC {
+    RT a;
+    float* chunk_state;   // [chunk slot, head, dim, vdim]; slot of chunk c of entry e = ent_row[e] / kChunk + e + c
+    int col_blocks;       // blocks of kChunkCols value columns; blockIdx.x = entry * col_blocks + column block
+};
+
+// rotated q (or k * k_scale * weight[j]) of a chunk into shared memory, rows padded to dim + 1
+__device__ __forceinline__ void stage_rotated(const RT& a, float* dst, int col_off, int h, int row0, int len, float mul, const float* rowmul) {
+    const int dim = a.dim, nf = a.rot_dims / 2;
+    for (int i = threadIdx.x; i < len * dim; i += blockDim.x) {
+        const int j = i / dim, d = i - j * dim;
+        const size_t r = (size_t)(row0 + j);
+        const float v = rotary_component(a.proj + r * a.ld_proj + col_off + h * dim, d, a.rot_dims, a.rot_layout, a.cos + r * nf, a.sin + r * nf);
+        dst[j * (dim + 1) + d] = v * mul * (rowmul ? rowmul[j] : 1.f);
+    }
+}
+
+template <int NACC>   // accumulators per thread: dim <= 4 * NACC
+__global__ void __launch_bounds__(256) retention_chunk_state_kernel(const RC rc) {
+    extern __shared__ float sm[];
+    const RT& a = rc.a;
+    const int e = blockIdx.x / rc.col_blocks, cb = blockIdx.x % rc.col_blocks;
+    const int c_in = blockIdx.y, h = blockIdx.z;
+    const int row_e = a.ent_row[e], n = a.ent_len[e];
+    if (c_in * kChunk >= n) return;
+    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim;
+    float* Kw = sm;                          // [kChunk][dim + 1], row j weighted by decay^(len-1-j)
+    float* pw = sm + kChunk * (dim + 1);     // [kChunk]
+    const float decay = a.decay[h];
+    for (int j = threadIdx.x; j < len; j += blockDim.x) pw[j] = powf(decay, (float)(len - 1 - j));
+    __syncthreads();
+    stage_rotated(a, Kw, a.k_off, h, row0, len, a.k_scale, pw);
+    __syncthreads();
+    const int c = cb * kChunkCols + (threadIdx.x & 63), dg = threadIdx.x >> 6;   // thread: one value column, rows dg, dg + 4, ...
+    float acc[NACC];
+#pragma unroll
+    for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+    if (c < a.vdim) {
+        for (int j = 0; j < len; ++j) {
+            const float v = a.proj[(size_t)(row0 + j) * a.ld_proj + a.v_off + h * a.vdim + c];
+            const float* kr = Kw + j * (dim + 1);
+#pragma unroll
+            for (int k = 0; k < NACC; ++k)
+                if (dg + 4 * k < dim) acc[k] = fmaf(kr[dg + 4 * k], v, acc[k]);
+        }
+        float* U = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
+#pragma unroll
+        for (int k = 0; k < NACC; ++k)
+            if (dg + 4 * k < dim) U[(size_t)(dg + 4 * k) * a.vdim] = acc[k];
+    }
+}
+
+// element-wise over (dim, vdim): walks the entry's chunks, leaves S at each chunk's start in place of its U
+__global__ void __launch_bounds__(256) retention_chunk_scan_kernel(const RC rc) {
+    const RT& a = rc.a;
+    const int e = blockIdx.x, h = blockIdx.y, i = blockIdx.z * blockDim.x + threadIdx.x;
+    const int per = a.dim * a.vdim;
+    if (i >= per) return;
+    const int row_e = a.ent_row[e], n = a.ent_len[e], b = a.slot[row_e], p0 = a.pos[row_e];
+    const float decay = a.decay[h];
+    float* sp = a.state + ((size_t)b * a.heads + h) * per + i;
+    float S = p0 > 0 ? *sp : 0.f;
+    const float full = powf(decay, (float)kChunk);
+    for (int c = 0; c * kChunk < n; ++c) {
+        const int len = min(kChunk, n - c * kChunk);
+        float* U = rc.chunk_state + ((size_t)(row_e / kChunk + e + c) * a.heads + h) * per + i;
+        const float u = *U;
+        *U = S;
+        S = fmaf(len == kChunk ? full : powf(decay, (float)len), S, u);
+    }
+    *sp = S;
+}
+
+__global__ void __launch_bounds__(256) retention_chunk_out_kernel(const RC rc) {
+    extern __shared__ float sm[];
+    const RT& a = rc.a;
+    const int e = blockIdx.x / rc.col_blocks, cb = blockIdx.x % rc.col_blocks;
+    const int c_in = blockIdx.y, h = blockIdx.z;
+    const int row_e = a.ent_row[e], n = a.ent_len[e];
+    if (c_in * kChunk >= n) return;
+    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim;
+    float* Qc = sm;                               // [kChunk][dim + 1]
+    float* Kc = Qc + kChunk * (dim + 1);          // [kChunk][dim + 1]
+    float* A = Kc + kChunk * (dim + 1);           // [kChunk][kChunk + 1]
+    float* pw = A + kChunk * (kChunk + 1);        // [kChunk + 1]: decay^k
+    const float decay = a.decay[h];
+    for (int k = threadIdx.x; k <= kChunk; k += blockDim.x) pw[k] = powf(decay, (float)k);
+    stage_rotated(a, Qc, a.q_off, h, row0, len, 1.f, nullptr);
+    stage_rotated(a, Kc, a.k_off, h, row0, len, a.k_scale, nullptr);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < kChunk * kChunk; idx += blockDim.x) {
+        const int i = idx / kChunk, j = idx % kChunk;
+        float v = 0.f;
+        if (j <= i && i < len) {
+            const float* q = Qc + i * (dim + 1);
+            const float* k = Kc + j * (dim + 1);
+            for (int d = 0; d < dim; ++d) v = fmaf(q[d], k[d], v);
+            v *= pw[i - j];
+        }
+        A[i * (kChunk + 1) + j] = v;
+    }
+    __syncthreads();
+    const int c = cb * kChunkCols + (threadIdx.x & 63), rg = threadIdx.x >> 6;   // thread: one value column, rows rg, rg + 4, ...
+    if (c >= a.vdim) return;
+    constexpr int NR = kChunk / 4;
+    float acc[NR], cross[NR];
+#pragma unroll
+    for (int k = 0; k < NR; ++k) acc[k] = cross[k] = 0.f;
+    for (int j = 0; j < len; ++j) {
+        const float v = a.proj[(size_t)(row0 + j) * a.ld_proj + a.v_off + h * a.vdim + c];
+#pragma unroll
+        for (int k = 0; k < NR; ++k) acc[k] = fmaf(A[(rg + 4 * k) * (kChunk + 1) + j], v, acc[k]);
+    }
+    const float* S = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
+    for (int d = 0; d < dim; ++d) {
+        const float s = S[(size_t)d * a.vdim];
+#pragma unroll
+        for (int k = 0; k < NR; ++k) cross[k] = fmaf(Qc[(rg + 4 * k) * (dim + 1) + d], s, cross[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < NR; ++k) {
+        const int i = rg + 4 * k;
+        if (i < len) a.out[(size_t)(row0 + i) * ((size_t)a.heads * a.vdim) + h * a.vdim + c] = fmaf(pw[i + 1], cross[k], acc[k]);
+    }
+}
+
 // one warp per (token, head)
 template <typename T>
 __global__ void unit_rms_gate_kernel(const float* __restrict__ o, const float* __restrict__ gate, long long ld_gate, T* __restrict__ out,
@@ -105,7 +244,10 @@ __global__ void unit_rms_gate_kernel(const float* __restrict__ o, const float* _
 
 using namespace b200;
 
-extern "C" size_t b200_retention_workspace_bytes(int, int, int, int, int) { return 0; }
+extern "C" size_t b200_retention_workspace_bytes(int n_tokens, int n_entries, int heads, int dim, int vdim) {
+    if (n_tokens < 2 * kChunk || n_entries < 1 || heads < 1 || dim < 1 || vdim < 1) return 0;
+    return (size_t)(n_tokens / kChunk + n_entries + 1) * heads * dim * vdim * sizeof(float);
+}
 
 extern "C" int b200_retention(const b200_retention_args* p, void* stream) {
     if (!p || !p->proj || !p->decay || !p->state || !p->out || !p->ent_row || !p->ent_len || !p->slot || !p->pos || p->n_entries < 0 ||
@@ -117,11 +259,36 @@ extern "C" int b200_retention(const b200_retention_args* p, void* stream) {
     if (p->n_entries == 0) return B200_OK;
     RT a{p->proj, p->ld_proj, p->q_off, p->k_off, p->v_off, p->cos, p->sin, p->rot_dims, p->rot_layout, p->decay, p->k_scale,
          p->state, p->out, p->ent_row, p->ent_len, p->slot, p->pos, p->heads, p->dim, p->vdim};
+    cudaStream_t s = (cudaStream_t)stream;
+    const char* env = getenv("B200_RETENTION_WALK");   // 1: every entry on the token-by-token kernel (debugging aid)
+    const size_t need = b200_retention_workspace_bytes(p->n_tokens, p->n_entries, p->heads, p->dim, p->vdim);
+    if (p->longest_entry >= 2 * kChunk && need > 0 && p->workspace && p->workspace_bytes >= need && !(env && env[0] == '1')) {
+        RC rc{a, reinterpret_cast<float*>(p->workspace), 1};
+        const int col_blocks = (p->vdim + kChunkCols - 1) / kChunkCols, chunks = (p->longest_entry + kChunk - 1) / kChunk;
+        if (chunks > 65535 || p->heads > 65535) return B200_EUNSUPPORTED;
+        const dim3 grid(p->n_entries * col_blocks, chunks, p->heads);
+        const size_t smem1 = ((size_t)kChunk * (p->dim + 1) + kChunk) * sizeof(float);
+        const size_t smem3 = ((size_t)2 * kChunk * (p->dim + 1) + kChunk * (kChunk + 1) + kChunk + 1) * sizeof(float);
+        static unsigned long long done1[4] = {0, 0, 0, 0}, done3 = 0;
+        // the attribute is set once per kernel: to the most any supported dim (256) needs
+        constexpr int kMax1 = (kChunk * 257 + kChunk) * 4, kMax3 = (2 * kChunk * 257 + kChunk * (kChunk + 1) + kChunk + 1) * 4;
+        cudaError_t e = ensure_max_dynamic_smem((const void*)retention_chunk_out_kernel, kMax3, done3);
+        if (e != cudaSuccess) return (int)e;
+        rc.col_blocks = col_blocks;
+        if (p->dim <= 32) { ensure_max_dynamic_smem((const void*)retention_chunk_state_kernel<8>, kMax1, done1[0]); retention_chunk_state_kernel<8><<<grid, 256, smem1, s>>>(rc); }
+        else if (p->dim <= 64) { ensure_max_dynamic_smem((const void*)retention_chunk_state_kernel<16>, kMax1, done1[1]); retention_chunk_state_kernel<16><<<grid, 256, smem1, s>>>(rc); }
+        else if (p->dim <= 128) { ensure_max_dynamic_smem((const void*)retention_chunk_state_kernel<32>, kMax1, done1[2]); retention_chunk_state_kernel<32><<<grid, 256, smem1, s>>>(rc); }
+        else { ensure_max_dynamic_smem((const void*)retention_chunk_state_kernel<64>, kMax1, done1[3]); retention_chunk_state_kernel<64><<<grid, 256, smem1, s>>>(rc); }
+        const int per = p->dim * p->vdim;
+        retention_chunk_scan_kernel<<<dim3(p->n_entries, p->heads, (per + 255) / 256), 256, 0, s>>>(rc);
+        retention_chunk_out_kernel<<<grid, 256, smem3, s>>>(rc);
+        count_launch(3);
+        return (int)cudaGetLastError();
+    }
     const int threads = p->vdim <= 32 ? 32 : p->vdim <= 64 ? 64 : 128;
     const dim3 grid(p->n_entries, p->heads, (p->vdim + threads - 1) / threads);
     if (grid.y > 65535 || grid.z > 65535) return B200_EUNSUPPORTED;
     const size_t smem = (size_t)(2 + 2 * kWalkTokens) * p->dim * sizeof(float);
-    cudaStream_t s = (cudaStream_t)stream;
     if (p->dim <= 32) retention_walk_kernel<32><<<grid, threads, smem, s>>>(a);
     else if (p->dim <= 64) retention_walk_kernel<64><<<grid, threads, smem, s>>>(a);
     else if (p->dim <= 128) retention_walk_kernel<128><<<grid, threads, smem, s>>>(a);

@@ -35,7 +35,8 @@ class PagedAttentionArgs(C.Structure):
     """mirror of ``b200_paged_attention_args``"""
     _fields_ = [("q", _vp), ("out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("pages", _vp), ("max_pages", _i), ("page_rows", _i),
                 ("slot", _vp), ("pos", _vp), ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("vdim", _i),
-                ("scale", _f), ("softcap", _f), ("denom_bias", _f), ("dtype", _i), ("longest_entry", _i)]
+                ("scale", _f), ("softcap", _f), ("denom_bias", _f), ("dtype", _i), ("longest_entry", _i),
+                ("longest_context", _i), ("workspace", _vp), ("workspace_bytes", _sz)]
 
 
 class RetentionArgs(C.Structure):
@@ -71,6 +72,7 @@ SERVE_PROTOTYPES = {
     "b200_rope_angles": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "b200_qk_prepare": (_i, [C.POINTER(QkPrepareArgs), _vp]),
     "b200_conv_state_update": (_i, [_vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
+    "b200_paged_attention_workspace_bytes": (_sz, [_i, _i, _i]),
     "b200_paged_attention": (_i, [C.POINTER(PagedAttentionArgs), _vp]),
     "b200_retention_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "b200_retention": (_i, [C.POINTER(RetentionArgs), _vp]),

@@ -207,8 +207,12 @@ def paged(S, code, k, v, PR, perm_seed):
 def run_attention(S, code, q, slot, pos, kp, vp, table, max_pages, PR, heads, kv, dim, vdim, scale, cap, bias, longest):
     T = len(slot)
     out = torch.empty(T, heads * vdim, dtype=tdt(S, code), device="cuda")
+    need = S.lib().b200_paged_attention_workspace_bytes(T, heads, vdim)
+    ws = torch.empty(max(need, 16), dtype=torch.uint8, device="cuda")
+    _alive.append(ws)
     a = S.PagedAttentionArgs(dev(q, tdt(S, code)).data_ptr(), out.data_ptr(), kp.data_ptr(), vp.data_ptr(), table.data_ptr(), max_pages, PR,
-                             ints(slot).data_ptr(), ints(pos).data_ptr(), T, heads, kv, dim, vdim, scale, cap, bias, code, longest)
+                             ints(slot).data_ptr(), ints(pos).data_ptr(), T, heads, kv, dim, vdim, scale, cap, bias, code, longest,
+                             max(pos) + 1, ws.data_ptr(), need)
     sync_ok(S.lib().b200_paged_attention(C.byref(a), None))
     return out.float().cpu()
 
