@@ -175,9 +175,9 @@ __device__ __forceinline__ void pa_ldsm_x4(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
-__device__ __forceinline__ void pa_ldsm_x2_trans(uint32_t (&r)[2], const void* p) {
+__device__ __forceinline__ void pa_ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];" : "=r"(r[0]), "=r"(r[1]) : "r"(a));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 __device__ __forceinline__ void pa_mma(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
     const float m0 = a.denom_bias > 0.f ? 0.f : -1e30f;
     float m_run[2] = {m0, m0}, l_run[2] = {a.denom_bias, a.denom_bias};
     const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;
+    const float two_over_cap = a.softcap > 0.f ? 2.0f / a.softcap : 0.f;
     const bf* Kp = reinterpret_cast<const bf*>(a.k_pool);
     const bf* Vp = reinterpret_cast<const bf*>(a.v_pool);
 
@@ -268,13 +269,15 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
 #pragma unroll
             for (int nt = 0; nt < kTileN / 8; ++nt) {
                 s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-                const bf* krow = Kb + (nt * 8 + gid) * RS + tig * 2;
+                // one ldmatrix.x4 brings the K fragments of two k steps: matrices (k 0-7 | 8-15 | 16-23 | 24-31) of 8 keys
+                const bf* kaddr = Kb + (nt * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ++ks) {
-                    uint32_t bfr[2];
-                    bfr[0] = *reinterpret_cast<const uint32_t*>(krow + ks * 16);
-                    bfr[1] = *reinterpret_cast<const uint32_t*>(krow + ks * 16 + 8);
-                    pa_mma(s[nt], qf[ks], bfr);
+                for (int ks = 0; ks < D / 16; ks += 2) {
+                    uint32_t b4[4];
+                    pa_ldsm_x4(b4, kaddr + ks * 16);
+                    const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+                    pa_mma(s[nt], qf[ks], b0);
+                    pa_mma(s[nt], qf[ks + 1], b1);
                 }
             }
             float mx[2] = {-INFINITY, -INFINITY};
@@ -284,7 +287,10 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
                 for (int e = 0; e < 4; ++e) {
                     const int j = k0 + nt * 8 + tig * 2 + (e & 1);
                     float v = s[nt][e] * a.scale;
-                    if (a.softcap > 0.f) v = a.softcap * tanhf(v / a.softcap);
+                    if (a.softcap > 0.f) {   // cap * tanh(v / cap) as (t - 1) / (t + 1), t = e^(2 v / cap): absolute error ~1e-7 * cap
+                        const float t = __expf(fminf(fmaxf(v * two_over_cap, -30.f), 30.f));
+                        v = a.softcap * __fdividef(t - 1.f, t + 1.f);
+                    }
                     v = j <= ((e & 2) ? p_hi : p_lo) ? v : -INFINITY;
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -295,7 +301,7 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
                 mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 1));
                 mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 2));
                 const float mn = fmaxf(m_run[hrow], mx[hrow]);   // finite: m starts at 0 (the sink) or at -1e30
-                alpha[hrow] = expf(m_run[hrow] - mn);
+                alpha[hrow] = __expf(m_run[hrow] - mn);
                 m_run[hrow] = mn;
             }
             float sum[2] = {0.f, 0.f};
@@ -303,7 +309,7 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
             for (int nt = 0; nt < kTileN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = expf(s[nt][e] - m_run[e >> 1]);   // masked: exp(-inf) = 0
+                    const float pv = __expf(s[nt][e] - m_run[e >> 1]);   // masked: exp(-inf) = 0
                     s[nt][e] = pv;
                     sum[e >> 1] += pv;
                 }
@@ -323,10 +329,12 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
                 pf[2] = pa_pack(s[2 * kk + 1][0], s[2 * kk + 1][1]);
                 pf[3] = pa_pack(s[2 * kk + 1][2], s[2 * kk + 1][3]);
 #pragma unroll
-                for (int nt = 0; nt < D / 8; ++nt) {
-                    uint32_t bfr[2];
-                    pa_ldsm_x2_trans(bfr, Vb + (kk * 16 + (lane & 15)) * RS + nt * 8);
-                    pa_mma(o[nt], pf, bfr);
+                for (int nt = 0; nt < D / 8; nt += 2) {   // one transposed ldmatrix.x4: the V fragments of two column tiles
+                    uint32_t b4[4];
+                    pa_ldsm_x4_trans(b4, Vb + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * RS + (nt + (lane >> 4)) * 8);
+                    const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+                    pa_mma(o[nt], pf, b0);
+                    pa_mma(o[nt + 1], pf, b1);
                 }
             }
         }

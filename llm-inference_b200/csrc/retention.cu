@@ -100,49 +100,62 @@ struct RC {
     int col_blocks;       // blocks of kChunkCols value columns; blockIdx.x = entry * col_blocks + column block
 };
 
-// rotated q (or k * k_scale * weight[j]) of a chunk into shared memory, rows padded to dim + 1
+__host__ __device__ __forceinline__ int chunk_row_stride(int dim) { return ((dim + 3) & ~3) + 4; }   // floats; rows stay 16-byte aligned
+
+// rotated q (or k * k_scale * weight[j]) of a chunk into shared memory; the padding columns are zero
 __device__ __forceinline__ void stage_rotated(const RT& a, float* dst, int col_off, int h, int row0, int len, float mul, const float* rowmul) {
-    const int dim = a.dim, nf = a.rot_dims / 2;
-    for (int i = threadIdx.x; i < len * dim; i += blockDim.x) {
-        const int j = i / dim, d = i - j * dim;
+    const int dim = a.dim, nf = a.rot_dims / 2, rs = chunk_row_stride(dim);
+    for (int i = threadIdx.x; i < len * rs; i += blockDim.x) {
+        const int j = i / rs, d = i - j * rs;
         const size_t r = (size_t)(row0 + j);
-        const float v = rotary_component(a.proj + r * a.ld_proj + col_off + h * dim, d, a.rot_dims, a.rot_layout, a.cos + r * nf, a.sin + r * nf);
-        dst[j * (dim + 1) + d] = v * mul * (rowmul ? rowmul[j] : 1.f);
+        float v = 0.f;
+        if (d < dim)
+            v = rotary_component(a.proj + r * a.ld_proj + col_off + h * dim, d, a.rot_dims, a.rot_layout, a.cos + r * nf, a.sin + r * nf) * mul *
+                (rowmul ? rowmul[j] : 1.f);
+        dst[i] = v;
     }
 }
 
-template <int NACC>   // accumulators per thread: dim <= 4 * NACC
+template <int NACC>   // accumulators per thread (a multiple of 4): dim <= 4 * NACC
 __global__ void __launch_bounds__(256) retention_chunk_state_kernel(const RC rc) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const RT& a = rc.a;
     const int e = blockIdx.x / rc.col_blocks, cb = blockIdx.x % rc.col_blocks;
     const int c_in = blockIdx.y, h = blockIdx.z;
     const int row_e = a.ent_row[e], n = a.ent_len[e];
     if (c_in * kChunk >= n) return;
-    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim;
-    float* Kw = sm;                          // [kChunk][dim + 1], row j weighted by decay^(len-1-j)
-    float* pw = sm + kChunk * (dim + 1);     // [kChunk]
+    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim, rs = chunk_row_stride(dim);
+    float* Kw = sm;                  // [kChunk][rs], row j weighted by decay^(len-1-j)
+    float* pw = sm + kChunk * rs;    // [kChunk]
     const float decay = a.decay[h];
     for (int j = threadIdx.x; j < len; j += blockDim.x) pw[j] = powf(decay, (float)(len - 1 - j));
     __syncthreads();
     stage_rotated(a, Kw, a.k_off, h, row0, len, a.k_scale, pw);
     __syncthreads();
-    const int c = cb * kChunkCols + (threadIdx.x & 63), dg = threadIdx.x >> 6;   // thread: one value column, rows dg, dg + 4, ...
+    // thread: one value column, NACC consecutive rows of the state (read from shared memory four at a time)
+    const int c = cb * kChunkCols + (threadIdx.x & 63), d0 = (threadIdx.x >> 6) * NACC, dpad = (dim + 3) & ~3;
     float acc[NACC];
 #pragma unroll
     for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
-    if (c < a.vdim) {
+    if (c < a.vdim && d0 < dim) {
+        const float* vcol = a.proj + (size_t)row0 * a.ld_proj + a.v_off + h * a.vdim + c;
         for (int j = 0; j < len; ++j) {
-            const float v = a.proj[(size_t)(row0 + j) * a.ld_proj + a.v_off + h * a.vdim + c];
-            const float* kr = Kw + j * (dim + 1);
+            const float v = vcol[(size_t)j * a.ld_proj];
+            const float* kr = Kw + j * rs + d0;
 #pragma unroll
-            for (int k = 0; k < NACC; ++k)
-                if (dg + 4 * k < dim) acc[k] = fmaf(kr[dg + 4 * k], v, acc[k]);
+            for (int k = 0; k < NACC; k += 4)
+                if (d0 + k < dpad) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kr + k);
+                    acc[k] = fmaf(k4.x, v, acc[k]);
+                    acc[k + 1] = fmaf(k4.y, v, acc[k + 1]);
+                    acc[k + 2] = fmaf(k4.z, v, acc[k + 2]);
+                    acc[k + 3] = fmaf(k4.w, v, acc[k + 3]);
+                }
         }
         float* U = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
 #pragma unroll
         for (int k = 0; k < NACC; ++k)
-            if (dg + 4 * k < dim) U[(size_t)(dg + 4 * k) * a.vdim] = acc[k];
+            if (d0 + k < dim) U[(size_t)(d0 + k) * a.vdim] = acc[k];
     }
 }
 
@@ -157,43 +170,56 @@ __global__ void __launch_bounds__(256) retention_chunk_scan_kernel(const RC rc) 
     float* sp = a.state + ((size_t)b * a.heads + h) * per + i;
     float S = p0 > 0 ? *sp : 0.f;
     const float full = powf(decay, (float)kChunk);
-    for (int c = 0; c * kChunk < n; ++c) {
-        const int len = min(kChunk, n - c * kChunk);
-        float* U = rc.chunk_state + ((size_t)(row_e / kChunk + e + c) * a.heads + h) * per + i;
-        const float u = *U;
-        *U = S;
-        S = fmaf(len == kChunk ? full : powf(decay, (float)len), S, u);
+    const int chunks = (n + kChunk - 1) / kChunk;
+    float* U = rc.chunk_state + ((size_t)(row_e / kChunk + e) * a.heads + h) * per + i;
+    const size_t step = (size_t)a.heads * per;
+    for (int c0 = 0; c0 < chunks; c0 += 8) {   // eight loads in flight, then the dependent chain
+        float u[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) u[k] = c0 + k < chunks ? U[(size_t)(c0 + k) * step] : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+            if (c0 + k < chunks) {
+                const int len = min(kChunk, n - (c0 + k) * kChunk);
+                U[(size_t)(c0 + k) * step] = S;
+                S = fmaf(len == kChunk ? full : powf(decay, (float)len), S, u[k]);
+            }
     }
     *sp = S;
 }
 
 __global__ void __launch_bounds__(256) retention_chunk_out_kernel(const RC rc) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     const RT& a = rc.a;
     const int e = blockIdx.x / rc.col_blocks, cb = blockIdx.x % rc.col_blocks;
     const int c_in = blockIdx.y, h = blockIdx.z;
     const int row_e = a.ent_row[e], n = a.ent_len[e];
     if (c_in * kChunk >= n) return;
-    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim;
-    float* Qc = sm;                               // [kChunk][dim + 1]
-    float* Kc = Qc + kChunk * (dim + 1);          // [kChunk][dim + 1]
-    float* A = Kc + kChunk * (dim + 1);           // [kChunk][kChunk + 1]
-    float* pw = A + kChunk * (kChunk + 1);        // [kChunk + 1]: decay^k
+    const int row0 = row_e + c_in * kChunk, len = min(kChunk, n - c_in * kChunk), dim = a.dim, rs = chunk_row_stride(dim);
+    constexpr int AS = kChunk + 4;                // row stride of A in floats
+    float* Qc = sm;                               // [kChunk][rs]
+    float* Kc = Qc + kChunk * rs;                 // [kChunk][rs]
+    float* A = Kc + kChunk * rs;                  // [kChunk][AS]
+    float* pw = A + kChunk * AS;                  // [kChunk + 1]: decay^k
     const float decay = a.decay[h];
     for (int k = threadIdx.x; k <= kChunk; k += blockDim.x) pw[k] = powf(decay, (float)k);
     stage_rotated(a, Qc, a.q_off, h, row0, len, 1.f, nullptr);
     stage_rotated(a, Kc, a.k_off, h, row0, len, a.k_scale, nullptr);
     __syncthreads();
+    const int dpad = (dim + 3) & ~3;
     for (int idx = threadIdx.x; idx < kChunk * kChunk; idx += blockDim.x) {
         const int i = idx / kChunk, j = idx % kChunk;
         float v = 0.f;
         if (j <= i && i < len) {
-            const float* q = Qc + i * (dim + 1);
-            const float* k = Kc + j * (dim + 1);
-            for (int d = 0; d < dim; ++d) v = fmaf(q[d], k[d], v);
+            const float* q = Qc + i * rs;
+            const float* k = Kc + j * rs;
+            for (int d = 0; d < dpad; d += 4) {
+                const float4 q4 = *reinterpret_cast<const float4*>(q + d), k4 = *reinterpret_cast<const float4*>(k + d);
+                v = fmaf(q4.x, k4.x, v); v = fmaf(q4.y, k4.y, v); v = fmaf(q4.z, k4.z, v); v = fmaf(q4.w, k4.w, v);
+            }
             v *= pw[i - j];
         }
-        A[i * (kChunk + 1) + j] = v;
+        A[i * AS + j] = v;
     }
     __syncthreads();
     const int c = cb * kChunkCols + (threadIdx.x & 63), rg = threadIdx.x >> 6;   // thread: one value column, rows rg, rg + 4, ...
@@ -202,16 +228,29 @@ __global__ void __launch_bounds__(256) retention_chunk_out_kernel(const RC rc) {
     float acc[NR], cross[NR];
 #pragma unroll
     for (int k = 0; k < NR; ++k) acc[k] = cross[k] = 0.f;
-    for (int j = 0; j < len; ++j) {
-        const float v = a.proj[(size_t)(row0 + j) * a.ld_proj + a.v_off + h * a.vdim + c];
+    const float* vcol = a.proj + (size_t)row0 * a.ld_proj + a.v_off + h * a.vdim + c;
+    for (int j = 0; j < len; j += 4) {
+        float v[4];
 #pragma unroll
-        for (int k = 0; k < NR; ++k) acc[k] = fmaf(A[(rg + 4 * k) * (kChunk + 1) + j], v, acc[k]);
+        for (int q = 0; q < 4; ++q) v[q] = j + q < len ? vcol[(size_t)(j + q) * a.ld_proj] : 0.f;
+#pragma unroll
+        for (int k = 0; k < NR; ++k) {
+            const float4 a4 = *reinterpret_cast<const float4*>(A + (rg + 4 * k) * AS + j);
+            acc[k] = fmaf(a4.x, v[0], acc[k]); acc[k] = fmaf(a4.y, v[1], acc[k]);
+            acc[k] = fmaf(a4.z, v[2], acc[k]); acc[k] = fmaf(a4.w, v[3], acc[k]);
+        }
     }
     const float* S = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
-    for (int d = 0; d < dim; ++d) {
-        const float s = S[(size_t)d * a.vdim];
+    for (int d = 0; d < dpad; d += 4) {
+        float sv[4];
 #pragma unroll
-        for (int k = 0; k < NR; ++k) cross[k] = fmaf(Qc[(rg + 4 * k) * (dim + 1) + d], s, cross[k]);
+        for (int q = 0; q < 4; ++q) sv[q] = d + q < dim ? S[(size_t)(d + q) * a.vdim] : 0.f;
+#pragma unroll
+        for (int k = 0; k < NR; ++k) {
+            const float4 q4 = *reinterpret_cast<const float4*>(Qc + (rg + 4 * k) * rs + d);
+            cross[k] = fmaf(q4.x, sv[0], cross[k]); cross[k] = fmaf(q4.y, sv[1], cross[k]);
+            cross[k] = fmaf(q4.z, sv[2], cross[k]); cross[k] = fmaf(q4.w, sv[3], cross[k]);
+        }
     }
 #pragma unroll
     for (int k = 0; k < NR; ++k) {
@@ -267,11 +306,12 @@ extern "C" int b200_retention(const b200_retention_args* p, void* stream) {
         const int col_blocks = (p->vdim + kChunkCols - 1) / kChunkCols, chunks = (p->longest_entry + kChunk - 1) / kChunk;
         if (chunks > 65535 || p->heads > 65535) return B200_EUNSUPPORTED;
         const dim3 grid(p->n_entries * col_blocks, chunks, p->heads);
-        const size_t smem1 = ((size_t)kChunk * (p->dim + 1) + kChunk) * sizeof(float);
-        const size_t smem3 = ((size_t)2 * kChunk * (p->dim + 1) + kChunk * (kChunk + 1) + kChunk + 1) * sizeof(float);
+        const int rs = chunk_row_stride(p->dim);
+        const size_t smem1 = ((size_t)kChunk * rs + kChunk) * sizeof(float);
+        const size_t smem3 = ((size_t)2 * kChunk * rs + kChunk * (kChunk + 4) + kChunk + 4) * sizeof(float);
         static unsigned long long done1[4] = {0, 0, 0, 0}, done3 = 0;
         // the attribute is set once per kernel: to the most any supported dim (256) needs
-        constexpr int kMax1 = (kChunk * 257 + kChunk) * 4, kMax3 = (2 * kChunk * 257 + kChunk * (kChunk + 1) + kChunk + 1) * 4;
+        constexpr int kMax1 = (kChunk * 260 + kChunk) * 4, kMax3 = (2 * kChunk * 260 + kChunk * (kChunk + 4) + kChunk + 4) * 4;
         cudaError_t e = ensure_max_dynamic_smem((const void*)retention_chunk_out_kernel, kMax3, done3);
         if (e != cudaSuccess) return (int)e;
         rc.col_blocks = col_blocks;
