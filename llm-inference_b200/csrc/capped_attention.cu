@@ -141,6 +141,178 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_row_kernel(const PA
     }
 }
 
+// Decode batches (few rows, long contexts): one CTA per (token, key head, share of the context) serves ALL query heads of
+// the group from one pass over the keys and values. Eight lanes share a key row (16-byte loads, a row is read once,
+// whole sectors), four keys per warp step; the scores of 32 keys go through shared memory to the softmax (a lane per
+// key) and on to the weighted value sum (a lane per pair of output columns). fp32 arithmetic on caches of either dtype.
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+    static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+};
+template <> struct Pair<__nv_bfloat16> {
+    static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+};
+
+template <typename T, int R>   // R query heads per key head
+__global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const PA a) {
+    extern __shared__ float sm[];
+    float* qs = sm;                                        // [R][dim]
+    float* sc = qs + R * a.dim;                            // [warps][R][32]
+    float* om = sc + kRowWarps * R * 32;                   // [warps][R][vdim]
+    __shared__ float ms[kRowWarps][R], ls[kRowWarps][R];
+    __shared__ unsigned long long rows[kRowWarps][32];
+    const int t = blockIdx.x, g = blockIdx.y, warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int p = a.pos[t], dim = a.dim, vdim = a.vdim;
+    const int* plist = a.pages + (size_t)a.slot[t] * a.max_pages;
+    const T* q = reinterpret_cast<const T*>(a.q) + ((size_t)t * a.heads + g * R) * dim;
+    for (int i = threadIdx.x; i < R * dim; i += blockDim.x) qs[i] = DT<T>::to_f(q[i]);
+    __syncthreads();
+    const T* K = reinterpret_cast<const T*>(a.k_pool);
+    const T* V = reinterpret_cast<const T*>(a.v_pool);
+    float m[R], l[R], o[R][4][2];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        const bool sink = warp == 0 && blockIdx.z == 0 && a.denom_bias > 0.f;
+        m[r] = sink ? 0.f : -INFINITY;
+        l[r] = sink ? a.denom_bias : 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[r][c][0] = o[r][c][1] = 0.f;
+    }
+    const int per = ((p + a.splits) / a.splits + 31) & ~31;
+    const int j_begin = blockIdx.z * per, j_end = min(p + 1, j_begin + per);
+    float* scw = sc + warp * R * 32;
+    const int l8 = lane & 7;
+    for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
+        for (int it = 0; it < 8; ++it) {   // scores of keys j0 + 4 it + (lane / 8)
+            const int kk = it * 4 + (lane >> 3), j = j0 + kk;
+            float acc[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) acc[r] = 0.f;
+            size_t row = 0;
+            if (j < j_end) {
+                row = ((size_t)plist[j / a.page_rows] * a.page_rows + j % a.page_rows) * a.kv_heads + g;
+                const T* kr = K + row * dim;
+                for (int i = l8 * 8; i < dim; i += 64) {
+                    float f[8];
+                    if constexpr (sizeof(T) == 2) {   // eight bfloat16 in one 16-byte load
+                        const Pack16 pk = ld16(kr + i);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&pk.w[e]));
+                            f[2 * e] = v.x;
+                            f[2 * e + 1] = v.y;
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; e += 4) {
+                            const Pack16 pk = ld16(kr + i + e);
+#pragma unroll
+                            for (int x = 0; x < 4; ++x) f[e + x] = __uint_as_float(pk.w[x]);
+                        }
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r)
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[r] = fmaf(qs[r * dim + i + e], f[e], acc[r]);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 1);
+                acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 2);
+                acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], 4);
+            }
+            if (l8 == 0) {
+                rows[warp][kk] = row;
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    float sv = acc[r] * a.scale;
+                    if (a.softcap > 0.f) sv = a.softcap * tanhf(sv / a.softcap);
+                    scw[r * 32 + kk] = j < j_end ? sv : -INFINITY;
+                }
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int r = 0; r < R; ++r) {   // softmax step, a lane per key
+            const float sv = scw[r * 32 + lane];
+            float bm = sv;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, d));
+            const float mn = fmaxf(m[r], bm);          // finite: the block holds at least one key
+            const float corr = expf(m[r] - mn);
+            const float pj = expf(sv - mn);            // a masked key: exp(-inf) = 0
+            float ps = pj;
+#pragma unroll
+            for (int d = 16; d > 0; d >>= 1) ps += __shfl_xor_sync(0xffffffffu, ps, d);
+            l[r] = l[r] * corr + ps;
+            m[r] = mn;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) { o[r][c][0] *= corr; o[r][c][1] *= corr; }
+            scw[r * 32 + lane] = pj;
+        }
+        __syncwarp();
+        const int n = min(32, j_end - j0);
+        for (int kk = 0; kk < n; ++kk) {   // weighted values, a lane per pair of columns
+            const T* vr = V + rows[warp][kk] * vdim;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int col = 2 * lane + 64 * c;
+                if (col < vdim) {
+                    const float2 v = Pair<T>::load(vr + col);
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const float pk = scw[r * 32 + kk];
+                        o[r][c][0] = fmaf(pk, v.x, o[r][c][0]);
+                        o[r][c][1] = fmaf(pk, v.y, o[r][c][1]);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        if (lane == 0) { ms[warp][r] = m[r]; ls[warp][r] = l[r]; }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int col = 2 * lane + 64 * c;
+            if (col < vdim) { om[(warp * R + r) * vdim + col] = o[r][c][0]; om[(warp * R + r) * vdim + col + 1] = o[r][c][1]; }
+        }
+    }
+    __syncthreads();
+    for (int r = 0; r < R; ++r) {
+        const int h = g * R + r;
+        float M = ms[0][r];
+        for (int w = 1; w < kRowWarps; ++w) M = fmaxf(M, ms[w][r]);
+        float L = 0.f;
+        for (int w = 0; w < kRowWarps; ++w) L += M == -INFINITY ? 0.f : ls[w][r] * expf(ms[w][r] - M);
+        float* pr = a.splits > 1 ? a.part + (((size_t)t * a.heads + h) * a.splits + blockIdx.z) * (vdim + 2) : nullptr;
+        if (pr && threadIdx.x == 0) { pr[0] = M; pr[1] = L; }
+        T* dst = reinterpret_cast<T*>(a.out) + ((size_t)t * a.heads + h) * vdim;
+        for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
+            float v = 0.f;
+            for (int w = 0; w < kRowWarps; ++w) v += M == -INFINITY ? 0.f : om[(w * R + r) * vdim + c] * expf(ms[w][r] - M);
+            if (pr) pr[2 + c] = v;
+            else dst[c] = DT<T>::from_f(v / L);
+        }
+    }
+}
+
+template <typename T>
+static bool launch_group(const PA& a, dim3 grid, cudaStream_t s) {
+    const int R = a.heads / a.kv_heads;
+    const size_t smem = ((size_t)R * a.dim + (size_t)kRowWarps * R * 32 + (size_t)kRowWarps * R * a.vdim) * sizeof(float);
+    if (smem > 48 * 1024) return false;
+    switch (R) {
+        case 1: paged_attn_group_kernel<T, 1><<<grid, kRowWarps * 32, smem, s>>>(a); return true;
+        case 2: paged_attn_group_kernel<T, 2><<<grid, kRowWarps * 32, smem, s>>>(a); return true;
+        case 4: paged_attn_group_kernel<T, 4><<<grid, kRowWarps * 32, smem, s>>>(a); return true;
+        case 8: paged_attn_group_kernel<T, 8><<<grid, kRowWarps * 32, smem, s>>>(a); return true;
+    }
+    return false;
+}
+
 // merges the shares of split contexts: one CTA per (token, head)
 template <typename T>
 __global__ void __launch_bounds__(128) paged_attn_combine_kernel(const float* __restrict__ part, T* __restrict__ out, int splits, int vdim) {
@@ -200,7 +372,8 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
     bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RS]
     int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RS);   // [64], -1: no such row
     int* row_slot = row_pos + kTileM;
-    const int t0 = blockIdx.x * kTileM, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+    // the last rows of a prompt see the most keys: those tiles are scheduled first, the short ones fill the tail
+    const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * kTileM, h = blockIdx.y, g = h / (a.heads / a.kv_heads);
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, gid = lane >> 2, tig = lane & 3;
     const int rows = min(kTileM, a.n_tokens - t0);
     for (int r = threadIdx.x; r < kTileM; r += blockDim.x) {
@@ -391,9 +564,15 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
         if (rc == 0) count_launch();
         return rc;
     }
+    // single tokens whose heads come in groups of 1, 2, 4 or 8 per key head: one pass over K / V serves the whole group
+    const int R = p->heads / p->kv_heads;
+    const bool group = p->longest_entry == 1 && (R == 1 || R == 2 || R == 4 || R == 8) && p->dim % 8 == 0 && p->vdim % 2 == 0 &&
+                       al16(p->k_pool) && al16(p->v_pool) && !(env && env[0] == '1') &&
+                       ((size_t)R * p->dim + (size_t)kRowWarps * R * (32 + p->vdim)) * sizeof(float) <= 48 * 1024;
+    const long long ctas = (long long)p->n_tokens * (group ? p->kv_heads : p->heads);
     // few rows with long contexts (decode batches): split every context over several CTAs and merge the shares
     if (p->longest_context > 256 && p->workspace && (long long)p->n_tokens * p->heads < 2 * sm_count()) {
-        int splits = (int)((4ll * sm_count() + (long long)p->n_tokens * p->heads - 1) / ((long long)p->n_tokens * p->heads));
+        int splits = (int)((4ll * sm_count() + ctas - 1) / ctas);
         splits = std::min(std::min(splits, kMaxSplits), (p->longest_context + 127) / 128);
         if (splits > 1 && p->workspace_bytes >= (size_t)p->n_tokens * p->heads * splits * (p->vdim + 2) * sizeof(float)) {
             a.splits = splits;
@@ -401,7 +580,13 @@ extern "C" int b200_paged_attention(const b200_paged_attention_args* p, void* st
         }
     }
     const dim3 grid3(p->n_tokens, p->heads, a.splits);
-    if (p->dtype == B200_BF16) paged_attn_row_kernel<__nv_bfloat16><<<grid3, kRowWarps * 32, smem, s>>>(a);
+    bool done = false;
+    if (group) {
+        const dim3 gridg(p->n_tokens, p->kv_heads, a.splits);
+        done = p->dtype == B200_BF16 ? launch_group<__nv_bfloat16>(a, gridg, s) : p->dtype == B200_F32 ? launch_group<float>(a, gridg, s) : false;
+    }
+    if (done) {
+    } else if (p->dtype == B200_BF16) paged_attn_row_kernel<__nv_bfloat16><<<grid3, kRowWarps * 32, smem, s>>>(a);
     else if (p->dtype == B200_F32) paged_attn_row_kernel<float><<<grid3, kRowWarps * 32, smem, s>>>(a);
     else return B200_EINVAL;
     count_launch();
