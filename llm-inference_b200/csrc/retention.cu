@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(128) retention_walk_kernel(const RT a) {
 // ---------------------------------------------------------------------------------------------------------------
 // chunk form
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kChunk = 64, kChunkCols = 64;
+constexpr int kChunk = 64, kColsPerThread = 2, kChunkCols = 64 * kColsPerThread;   // a thread owns columns c, c + 64
 
 struct RC {
     RT a;
@@ -132,30 +132,40 @@ __global__ void __launch_bounds__(256) retention_chunk_state_kernel(const RC rc)
     __syncthreads();
     stage_rotated(a, Kw, a.k_off, h, row0, len, a.k_scale, pw);
     __syncthreads();
-    // thread: one value column, NACC consecutive rows of the state (read from shared memory four at a time)
+    // thread: kColsPerThread value columns, NACC consecutive rows of the state (read from shared memory four at a time)
     const int c = cb * kChunkCols + (threadIdx.x & 63), d0 = (threadIdx.x >> 6) * NACC, dpad = (dim + 3) & ~3;
-    float acc[NACC];
+    float acc[kColsPerThread][NACC];
 #pragma unroll
-    for (int k = 0; k < NACC; ++k) acc[k] = 0.f;
+    for (int q = 0; q < kColsPerThread; ++q)
+#pragma unroll
+        for (int k = 0; k < NACC; ++k) acc[q][k] = 0.f;
     if (c < a.vdim && d0 < dim) {
         const float* vcol = a.proj + (size_t)row0 * a.ld_proj + a.v_off + h * a.vdim + c;
         for (int j = 0; j < len; ++j) {
-            const float v = vcol[(size_t)j * a.ld_proj];
+            float v[kColsPerThread];
+#pragma unroll
+            for (int q = 0; q < kColsPerThread; ++q) v[q] = c + 64 * q < a.vdim ? vcol[(size_t)j * a.ld_proj + 64 * q] : 0.f;
             const float* kr = Kw + j * rs + d0;
 #pragma unroll
             for (int k = 0; k < NACC; k += 4)
                 if (d0 + k < dpad) {
                     const float4 k4 = *reinterpret_cast<const float4*>(kr + k);
-                    acc[k] = fmaf(k4.x, v, acc[k]);
-                    acc[k + 1] = fmaf(k4.y, v, acc[k + 1]);
-                    acc[k + 2] = fmaf(k4.z, v, acc[k + 2]);
-                    acc[k + 3] = fmaf(k4.w, v, acc[k + 3]);
+#pragma unroll
+                    for (int q = 0; q < kColsPerThread; ++q) {
+                        acc[q][k] = fmaf(k4.x, v[q], acc[q][k]);
+                        acc[q][k + 1] = fmaf(k4.y, v[q], acc[q][k + 1]);
+                        acc[q][k + 2] = fmaf(k4.z, v[q], acc[q][k + 2]);
+                        acc[q][k + 3] = fmaf(k4.w, v[q], acc[q][k + 3]);
+                    }
                 }
         }
         float* U = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
 #pragma unroll
-        for (int k = 0; k < NACC; ++k)
-            if (d0 + k < dim) U[(size_t)(d0 + k) * a.vdim] = acc[k];
+        for (int q = 0; q < kColsPerThread; ++q)
+            if (c + 64 * q < a.vdim)
+#pragma unroll
+                for (int k = 0; k < NACC; ++k)
+                    if (d0 + k < dim) U[(size_t)(d0 + k) * a.vdim + 64 * q] = acc[q][k];
     }
 }
 
@@ -222,41 +232,56 @@ __global__ void __launch_bounds__(256) retention_chunk_out_kernel(const RC rc) {
         A[i * AS + j] = v;
     }
     __syncthreads();
-    const int c = cb * kChunkCols + (threadIdx.x & 63), rg = threadIdx.x >> 6;   // thread: one value column, rows rg, rg + 4, ...
+    const int c = cb * kChunkCols + (threadIdx.x & 63), rg = threadIdx.x >> 6;   // thread: columns c, c + 64; rows rg, rg + 4, ...
     if (c >= a.vdim) return;
-    constexpr int NR = kChunk / 4;
-    float acc[NR], cross[NR];
+    constexpr int NR = kChunk / 4, CP = kColsPerThread;
+    float acc[CP][NR], cross[CP][NR];
 #pragma unroll
-    for (int k = 0; k < NR; ++k) acc[k] = cross[k] = 0.f;
+    for (int q = 0; q < CP; ++q)
+#pragma unroll
+        for (int k = 0; k < NR; ++k) acc[q][k] = cross[q][k] = 0.f;
     const float* vcol = a.proj + (size_t)row0 * a.ld_proj + a.v_off + h * a.vdim + c;
     for (int j = 0; j < len; j += 4) {
-        float v[4];
+        float v[CP][4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) v[q] = j + q < len ? vcol[(size_t)(j + q) * a.ld_proj] : 0.f;
+        for (int q = 0; q < CP; ++q)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) v[q][x] = (j + x < len && c + 64 * q < a.vdim) ? vcol[(size_t)(j + x) * a.ld_proj + 64 * q] : 0.f;
 #pragma unroll
         for (int k = 0; k < NR; ++k) {
             const float4 a4 = *reinterpret_cast<const float4*>(A + (rg + 4 * k) * AS + j);
-            acc[k] = fmaf(a4.x, v[0], acc[k]); acc[k] = fmaf(a4.y, v[1], acc[k]);
-            acc[k] = fmaf(a4.z, v[2], acc[k]); acc[k] = fmaf(a4.w, v[3], acc[k]);
+#pragma unroll
+            for (int q = 0; q < CP; ++q) {
+                acc[q][k] = fmaf(a4.x, v[q][0], acc[q][k]); acc[q][k] = fmaf(a4.y, v[q][1], acc[q][k]);
+                acc[q][k] = fmaf(a4.z, v[q][2], acc[q][k]); acc[q][k] = fmaf(a4.w, v[q][3], acc[q][k]);
+            }
         }
     }
     const float* S = rc.chunk_state + (((size_t)(row_e / kChunk + e + c_in) * a.heads + h) * dim) * a.vdim + c;
     for (int d = 0; d < dpad; d += 4) {
-        float sv[4];
+        float sv[CP][4];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) sv[q] = d + q < dim ? S[(size_t)(d + q) * a.vdim] : 0.f;
+        for (int q = 0; q < CP; ++q)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) sv[q][x] = (d + x < dim && c + 64 * q < a.vdim) ? S[(size_t)(d + x) * a.vdim + 64 * q] : 0.f;
 #pragma unroll
         for (int k = 0; k < NR; ++k) {
             const float4 q4 = *reinterpret_cast<const float4*>(Qc + (rg + 4 * k) * rs + d);
-            cross[k] = fmaf(q4.x, sv[0], cross[k]); cross[k] = fmaf(q4.y, sv[1], cross[k]);
-            cross[k] = fmaf(q4.z, sv[2], cross[k]); cross[k] = fmaf(q4.w, sv[3], cross[k]);
+#pragma unroll
+            for (int q = 0; q < CP; ++q) {
+                cross[q][k] = fmaf(q4.x, sv[q][0], cross[q][k]); cross[q][k] = fmaf(q4.y, sv[q][1], cross[q][k]);
+                cross[q][k] = fmaf(q4.z, sv[q][2], cross[q][k]); cross[q][k] = fmaf(q4.w, sv[q][3], cross[q][k]);
+            }
         }
     }
 #pragma unroll
-    for (int k = 0; k < NR; ++k) {
-        const int i = rg + 4 * k;
-        if (i < len) a.out[(size_t)(row0 + i) * ((size_t)a.heads * a.vdim) + h * a.vdim + c] = fmaf(pw[i + 1], cross[k], acc[k]);
-    }
+    for (int q = 0; q < CP; ++q)
+#pragma unroll
+        for (int k = 0; k < NR; ++k) {
+            const int i = rg + 4 * k;
+            if (i < len && c + 64 * q < a.vdim)
+                a.out[(size_t)(row0 + i) * ((size_t)a.heads * a.vdim) + h * a.vdim + c + 64 * q] = fmaf(pw[i + 1], cross[q][k], acc[q][k]);
+        }
 }
 
 // one warp per (token, head)

@@ -31,25 +31,30 @@ struct QkPrep {
     int heads, kv_heads, dim;
 };
 
-// grid (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads. One thread per
-// dimension (strided when dim > blockDim).
+// One warp per (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads; a lane owns the
+// dimensions lane, lane + 32, ... (coalesced loads and stores); the head's sum of squares is a warp reduction and the
+// rotation reads its partner through the warp's slice of shared memory, so no CTA-wide barrier is needed.
+constexpr int kPrepWarps = 4;
 template <typename T>
-__global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrep a) {
-    extern __shared__ float vals[];   // [dim]: the normed head before rotation
-    __shared__ float red[4];
-    const int t = blockIdx.x, u = blockIdx.y, dim = a.dim;
+__global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPrep a, int n_units) {
+    extern __shared__ float prep_sm[];
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32, dim = a.dim;
+    const int unit = blockIdx.x * kPrepWarps + warp, per_token = a.heads + a.kv_heads;
+    if (unit >= n_units) return;
+    float* vals = prep_sm + warp * dim;   // the normed head before rotation
+    const int t = unit / per_token, u = unit % per_token;
     const bool is_k = u >= a.heads;
     const int ch0 = u * dim;          // first channel of this head in [q channels | k channels]
-    const int channels = (a.heads + a.kv_heads) * dim;
+    const int channels = per_token * dim;
     const int p = a.pos[t], b = a.slot[t];
     size_t cache_row = 0;
     if (is_k) cache_row = ((size_t)a.pages[(size_t)b * a.max_pages + p / a.page_rows] * a.page_rows + p % a.page_rows) * a.kv_heads + (u - a.heads);
+    const int first = a.conv_w ? a.start[t] : 0, taps = a.taps;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    for (int i = lane; i < dim; i += 32) {
         const int c = ch0 + i;
         float y;
         if (a.conv_w) {
-            const int first = a.start[t], taps = a.taps;
             y = 0.f;
             for (int j = 0; j < taps; ++j) {
                 const int back = taps - 1 - j, src = p - back;
@@ -65,21 +70,16 @@ __global__ void __launch_bounds__(128) qk_prepare_kernel(const QkPrep a) {
         ss += y * y;
     }
     const float* nw = is_k ? a.k_norm : a.q_norm;
-    float rinv = 1.f;
     if (nw) {
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (threadIdx.x % 32 == 0) red[threadIdx.x / 32] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int k = 0; k < (int)blockDim.x / 32; ++k) tot += red[k];
-        rinv = 1.0f / sqrtf(tot / (float)dim + a.eps);
-        for (int i = threadIdx.x; i < dim; i += blockDim.x) vals[i] = vals[i] * rinv * nw[i];
+        const float rinv = 1.0f / sqrtf(ss / (float)dim + a.eps);
+        for (int i = lane; i < dim; i += 32) vals[i] = vals[i] * rinv * nw[i];
     }
-    __syncthreads();
+    __syncwarp();
     const int nf = a.rot_dims / 2;
     T* dst = is_k ? reinterpret_cast<T*>(a.k_pool) + cache_row * dim : reinterpret_cast<T*>(a.q_out) + ((size_t)t * a.heads + u) * dim;
-    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+    for (int i = lane; i < dim; i += 32)
         dst[i] = DT<T>::from_f(rotary_component(vals, i, a.rot_dims, a.rot_layout, a.cos + (size_t)t * nf, a.sin + (size_t)t * nf));
 }
 
@@ -119,13 +119,14 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
              p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
              p->start, p->heads, p->kv_heads, p->dim};
     if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
-    const dim3 grid(p->n_tokens, p->heads + p->kv_heads);
-    const int threads = p->dim <= 32 ? 32 : p->dim <= 64 ? 64 : 128;
-    const size_t smem = (size_t)p->dim * sizeof(float);
+    const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads);
+    if (units > 0x7fffffffll) return B200_EUNSUPPORTED;
+    const unsigned grid = (unsigned)((units + kPrepWarps - 1) / kPrepWarps);
+    const size_t smem = (size_t)kPrepWarps * p->dim * sizeof(float);
     if (smem > 48 * 1024) return B200_EUNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
-    if (p->dtype == B200_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, threads, smem, s>>>(a);
-    else if (p->dtype == B200_F32) qk_prepare_kernel<float><<<grid, threads, smem, s>>>(a);
+    if (p->dtype == B200_BF16) qk_prepare_kernel<__nv_bfloat16><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
+    else if (p->dtype == B200_F32) qk_prepare_kernel<float><<<grid, kPrepWarps * 32, smem, s>>>(a, (int)units);
     else return B200_EINVAL;
     count_launch();
     return (int)cudaGetLastError();
