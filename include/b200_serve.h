@@ -112,6 +112,10 @@ int b200_layernorm_residual(float* x, const float* y, int n_rows, int width, flo
                             const float* b, const float* w2, const float* b2, void* out2, int out_dtype, void* stream);
 /* out[t, 0:width] = a[t,:], out[t, width:2 width] = b[t,:], as out_dtype (the operand of a projection of two streams) */
 int b200_concat_cast(const float* a, const float* b, void* out, int n_rows, int width, int out_dtype, void* stream);
+/* out[t, j] = act(gu[t, j]) * gu[t, n + j], act by epi (B200_GG_GLU: silu, B200_GG_GLU_GELU: tanh-gelu); gu fp32 [n_rows, 2 n]:
+ * the GLU of a [gate | up] product computed without the fused epilogue (small batches, where the stacked weight streams
+ * once through the split-K GEMM) */
+int b200_glu_act(const float* gu, void* out, int n_rows, int n, int epi, int out_dtype, void* stream);
 /* v[i] <- cap * tanh(v[i] / cap) */
 int b200_softcap(float* v, size_t n, float cap, void* stream);
 

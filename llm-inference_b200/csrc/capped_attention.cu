@@ -398,7 +398,7 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
     const float m0 = a.denom_bias > 0.f ? 0.f : -1e30f;
     float m_run[2] = {m0, m0}, l_run[2] = {a.denom_bias, a.denom_bias};
     const int r_lo = warp * 16 + gid, r_hi = r_lo + 8;
-    const float two_over_cap = a.softcap > 0.f ? 2.0f / a.softcap : 0.f;
+    const float scale_over_cap = a.softcap > 0.f ? a.scale / a.softcap : 0.f;
     const bf* Kp = reinterpret_cast<const bf*>(a.k_pool);
     const bf* Vp = reinterpret_cast<const bf*>(a.v_pool);
 
@@ -453,18 +453,45 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
                     pa_mma(s[nt], qf[ks + 1], b1);
                 }
             }
+            // cap * tanh(v / cap): when every score of this thread's tile is small against the cap (the usual case) the odd
+            // series x - x^3/3 + 2x^5/15 - 17x^7/315 is exact to fp32 rounding below |x| = 0.25 and costs no special-function
+            // unit; otherwise (t - 1) / (t + 1) with t = e^(2x) (absolute error ~1e-7 * cap)
+            if (a.softcap > 0.f) {
+                float big = 0.f;
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) { s[nt][e] *= scale_over_cap; big = fmaxf(big, fabsf(s[nt][e])); }
+                if (__all_sync(0xffffffffu, big < 0.25f)) {
+#pragma unroll
+                    for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float x = s[nt][e], x2 = x * x;
+                            s[nt][e] = a.softcap * x * fmaf(x2, fmaf(x2, fmaf(x2, -17.f / 315.f, 2.f / 15.f), -1.f / 3.f), 1.f);
+                        }
+                } else {
+#pragma unroll
+                    for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float t = __expf(fminf(fmaxf(2.f * s[nt][e], -30.f), 30.f));
+                            s[nt][e] = a.softcap * __fdividef(t - 1.f, t + 1.f);
+                        }
+                }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] *= a.scale;
+            }
             float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
             for (int nt = 0; nt < kTileN / 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int j = k0 + nt * 8 + tig * 2 + (e & 1);
-                    float v = s[nt][e] * a.scale;
-                    if (a.softcap > 0.f) {   // cap * tanh(v / cap) as (t - 1) / (t + 1), t = e^(2 v / cap): absolute error ~1e-7 * cap
-                        const float t = __expf(fminf(fmaxf(v * two_over_cap, -30.f), 30.f));
-                        v = a.softcap * __fdividef(t - 1.f, t + 1.f);
-                    }
-                    v = j <= ((e & 2) ? p_hi : p_lo) ? v : -INFINITY;
+                    const float v = j <= ((e & 2) ? p_hi : p_lo) ? s[nt][e] : -INFINITY;
                     s[nt][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }

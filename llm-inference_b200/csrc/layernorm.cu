@@ -112,6 +112,17 @@ __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __r
     }
 }
 
+// out[t, j] = act(gu[t, j]) * gu[t, n + j] (act: silu or gelu in its tanh form): the GLU of a [gate | up] product that was
+// computed without the fused epilogue (small batches stream the stacked weight once through the split-K GEMM)
+template <typename T>
+__global__ void glu_act_kernel(const float* __restrict__ gu, T* __restrict__ out, int n, size_t total, int gelu) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / n, j = i - t * n;
+    const float g = gu[t * 2 * n + j], u = gu[t * 2 * n + n + j];
+    out[i] = DT<T>::from_f((gelu ? gelu_tanh_f(g) : g / (1.f + expf(-g))) * u);
+}
+
 __global__ void softcap_kernel(float* __restrict__ v, size_t n, float cap) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) v[i] = cap * tanhf(v[i] / cap);
@@ -149,6 +160,19 @@ extern "C" int b200_concat_cast(const float* a, const float* b, void* out, int n
     cudaStream_t s = (cudaStream_t)stream;
     if (out_dtype == B200_BF16) concat_cast_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>(a, b, (__nv_bfloat16*)out, width);
     else if (out_dtype == B200_F32) concat_cast_kernel<float><<<n_rows, 256, 0, s>>>(a, b, (float*)out, width);
+    else return B200_EINVAL;
+    count_launch();
+    return (int)cudaGetLastError();
+}
+
+extern "C" int b200_glu_act(const float* gu, void* out, int n_rows, int n, int epi, int out_dtype, void* stream) {
+    if (!gu || !out || n_rows < 0 || n < 1 || (epi != B200_GG_GLU && epi != B200_GG_GLU_GELU)) return B200_EINVAL;
+    if (n_rows == 0) return B200_OK;
+    const size_t total = (size_t)n_rows * n;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dtype == B200_BF16) glu_act_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(gu, (__nv_bfloat16*)out, n, total, epi == B200_GG_GLU_GELU);
+    else if (out_dtype == B200_F32) glu_act_kernel<float><<<grid, 256, 0, s>>>(gu, (float*)out, n, total, epi == B200_GG_GLU_GELU);
     else return B200_EINVAL;
     count_launch();
     return (int)cudaGetLastError();

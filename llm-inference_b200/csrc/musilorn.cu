@@ -37,6 +37,7 @@ namespace b200 {
 namespace {
 
 constexpr int kPageRows = 64;
+constexpr int kStreamRows = 256;   // up to here b200_linear_ex streams weights through its M axis (split-K)
 constexpr double kPi = 3.14159265358979323846;
 
 struct MuRot {
@@ -141,6 +142,7 @@ private:
     void* attn_ws_ = nullptr;   // shares of split attention contexts / chunk states of retention
     size_t attn_ws_bytes_ = 0;
     int cap_T_ = 0, cap_W_ = 0;
+    float *gu_ = nullptr;   // [gate | up] of small batches before the activation
     float *x_ = nullptr, *x0_ = nullptr, *proj_ = nullptr, *y_ = nullptr, *ret_ = nullptr, *logits_ = nullptr, *cs_ = nullptr;
     void *h1_ = nullptr, *h2_ = nullptr, *cat_ = nullptr, *q_ = nullptr, *att_ = nullptr, *act_ = nullptr, *hf_ = nullptr;
     int* ids_dev_ = nullptr;
@@ -402,6 +404,7 @@ int Musilorn::ensure_scratch(int T, int W) {
         al(t * std::max(1, max_ff_) * E),          // act
         al((size_t)cW * D_ * E),                   // hf
         al((size_t)cW * 4),                        // ids
+        al((size_t)std::min(cT, kStreamRows) * 2 * std::max(1, max_ff_) * 4),   // gu
     };
     size_t total = 0;
     for (size_t s : sizes) total += s;
@@ -410,7 +413,7 @@ int Musilorn::ensure_scratch(int T, int W) {
     int k = 0;
     auto take = [&](auto*& dst) { dst = reinterpret_cast<std::remove_reference_t<decltype(dst)>>(p); p += sizes[k++]; };
     take(x_); take(x0_); take(proj_); take(y_); take(ret_); take(logits_); take(cs_);
-    take(h1_); take(h2_); take(cat_); take(q_); take(att_); take(act_); take(hf_); take(ids_dev_);
+    take(h1_); take(h2_); take(cat_); take(q_); take(att_); take(act_); take(hf_); take(ids_dev_); take(gu_);
     cap_T_ = cT;
     cap_W_ = cW;
     const size_t lf = (size_t)cW * vocab_;
@@ -541,7 +544,11 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
         const MuLayer* next = (r + 1 < runs_.size() && !runs_[r + 1].pass_start) ? &layers_[runs_[r + 1].layer] : nullptr;
         if (L.has_mlp) {
             MU_OP(b200_layernorm_residual(x_, y_, T, D, eps_, mult_, L.n1bw, L.n1bb, L.n2w, L.n2b, h2_, dt, stream_));
-            MU_OP(gemm(h2_, L.w_gu, act_, dt, T, L.ff, D, B200_GG_GLU_GELU));
+            if (dt == B200_BF16 && T <= kStreamRows) {   // few rows: the stacked [gate; up] streams once through the split-K GEMM
+                MU_OP(gemm(h2_, L.w_gu, gu_, B200_F32, T, 2 * L.ff, D));
+                MU_OP(b200_glu_act(gu_, act_, T, L.ff, B200_GG_GLU_GELU, dt, stream_));
+            } else
+                MU_OP(gemm(h2_, L.w_gu, act_, dt, T, L.ff, D, B200_GG_GLU_GELU));
             MU_OP(gemm(act_, L.w_down, y_, B200_F32, T, D, L.ff));
             MU_OP(b200_layernorm_residual(x_, y_, T, D, eps_, mult_, L.n2bw, L.n2bb, next ? next->n1w : nullptr, next ? next->n1b : nullptr,
                                           next ? h1_ : nullptr, dt, stream_));

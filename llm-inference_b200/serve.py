@@ -69,6 +69,7 @@ SERVE_PROTOTYPES = {
     "b200_layernorm_residual": (_i, [_vp, _vp, _i, _i, _f, _f, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "b200_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "b200_softcap": (_i, [_vp, _sz, _f, _vp]),
+    "b200_glu_act": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "b200_rope_angles": (_i, [_vp, _i, _vp, _i, _vp, _vp, _vp]),
     "b200_qk_prepare": (_i, [C.POINTER(QkPrepareArgs), _vp]),
     "b200_conv_state_update": (_i, [_vp, _ll, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),

@@ -358,3 +358,10 @@ def test_glu_with_tanh_gelu_in_the_gemm_epilogue(S, M, N, K, kind):
                                    S.GG_GLU_GELU, None, 0, None))
     want = O.gelu_tanh(x.double() @ w[:N].double().T) * (x.double() @ w[N:].double().T)
     assert rel(out.float(), want) < (2e-2 if kind == "bf16" else 2e-5)
+    # the unfused form of small batches: plain product, then the activation kernel
+    gu = dev((x @ w.T).float())
+    out2 = torch.empty(M, N, dtype=tdt(S, code), device="cuda")
+    sync_ok(S.lib().b200_glu_act(gu.data_ptr(), out2.data_ptr(), M, N, S.GG_GLU_GELU, code, None))
+    assert rel(out2.float(), want) < (2e-2 if kind == "bf16" else 2e-5)
+    sync_ok(S.lib().b200_glu_act(gu.data_ptr(), out2.data_ptr(), M, N, S.GG_GLU, code, None))
+    assert rel(out2.float(), O.silu(x.double() @ w[:N].double().T) * (x.double() @ w[N:].double().T)) < (2e-2 if kind == "bf16" else 2e-5)
