@@ -147,6 +147,8 @@ typedef struct b200_qk_prepare_args {
     const int* pages; int max_pages, page_rows;
     const int* slot; const int* pos; const int* start;
     int n_tokens, heads, kv_heads, dim, dtype;
+    int update_state_inline;   /* 1 (only when EVERY sequence brings exactly one token): the launch also files the token's
+                                  inputs in conv_state, and b200_conv_state_update is not needed */
 } b200_qk_prepare_args;
 int b200_qk_prepare(const b200_qk_prepare_args* a, void* stream);
 /* The last taps-1 inputs of every sequence of the step go to their ring places (end[t] = the sequence's length after

@@ -183,7 +183,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
     float* scw = sc + warp * R * 32;
     const int l8 = lane & 7;
     for (int j0 = j_begin + warp * 32; j0 < j_end; j0 += kRowWarps * 32) {
-        for (int it = 0; it < 8; ++it) {   // scores of keys j0 + 4 it + (lane / 8)
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {   // scores of keys j0 + 4 it + (lane / 8); unrolled: the loads of all steps are in flight together
             const int kk = it * 4 + (lane >> 3), j = j0 + kk;
             float acc[R];
 #pragma unroll
@@ -253,6 +254,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) paged_attn_group_kernel(const 
         }
         __syncwarp();
         const int n = min(32, j_end - j0);
+#pragma unroll 4
         for (int kk = 0; kk < n; ++kk) {   // weighted values, a lane per pair of columns
             const T* vr = V + rows[warp][kk] * vdim;
 #pragma unroll
@@ -362,14 +364,15 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi) {
 }
 
 template <int D>   // dim == vdim == D
-__global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
+__global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(const PA a) {
     using bf = __nv_bfloat16;
     constexpr int RS = D + 8;                 // row stride in elements: 16-byte aligned, conflict-free fragment loads
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     extern __shared__ __align__(16) unsigned char pa_smem[];
-    bf* Qs = reinterpret_cast<bf*>(pa_smem);                  // [64][RS]
-    bf* Ks = Qs + kTileM * RS;                                // [2][64][RS]
+    bf* Ks = reinterpret_cast<bf*>(pa_smem);                  // [2][64][RS]
     bf* Vs = Ks + 2 * kTileN * RS;                            // [2][64][RS]
+    bf* Qs = Ks + kTileN * RS;                                // [64][RS]: the Q tile borrows the second K buffer until its
+                                                              // fragments are in registers (three CTAs fit an SM this way)
     int* row_pos = reinterpret_cast<int*>(Vs + 2 * kTileN * RS);   // [64], -1: no such row
     int* row_slot = row_pos + kTileM;
     // the last rows of a prompt see the most keys: those tiles are scheduled first, the short ones fill the tail
@@ -555,7 +558,8 @@ __global__ void __launch_bounds__(128) paged_attn_tile_kernel(const PA a) {
 
 template <int D>
 static int launch_tile(const PA& a, cudaStream_t s) {
-    constexpr int smem = (kTileM + 4 * kTileN) * (D + 8) * 2 + 2 * kTileM * 4;
+    static_assert(kTileM == kTileN, "the Q tile borrows a K buffer");
+    constexpr int smem = 4 * kTileN * (D + 8) * 2 + 2 * kTileM * 4;
     static unsigned long long done = 0;
     const cudaError_t e = ensure_max_dynamic_smem((const void*)paged_attn_tile_kernel<D>, smem, done);
     if (e != cudaSuccess) return (int)e;

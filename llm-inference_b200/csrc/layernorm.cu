@@ -103,6 +103,65 @@ __global__ void __launch_bounds__(256) layernorm_residual_kernel(float* __restri
     for (int c = threadIdx.x; c < width; c += blockDim.x) out2[base + c] = DT<T>::from_f((row[c] - mean) * rstd * w2[c] + b2[c]);
 }
 
+// the same for rows of at most 256 * kLnPerThread values: the row and every weight are loaded up front (one round trip to
+// memory instead of three) and live in registers
+constexpr int kLnPerThread = 8;
+template <typename T>
+__global__ void __launch_bounds__(256) layernorm_residual_reg_kernel(float* __restrict__ x, const float* __restrict__ y, int width,
+                                                                     float eps, float mult, const float* __restrict__ w,
+                                                                     const float* __restrict__ b, const float* __restrict__ w2,
+                                                                     const float* __restrict__ b2, T* __restrict__ out2) {
+    __shared__ float red[8];
+    const size_t base = (size_t)blockIdx.x * width;
+    float xv[kLnPerThread], yv[kLnPerThread], wv[kLnPerThread], bv[kLnPerThread], w2v[kLnPerThread], b2v[kLnPerThread];
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) {
+        const int c = threadIdx.x + 256 * k;
+        const bool in = c < width;
+        yv[k] = in ? y[base + c] : 0.f;
+        xv[k] = in ? x[base + c] : 0.f;
+        wv[k] = in ? w[c] : 0.f;
+        bv[k] = in ? b[c] : 0.f;
+        w2v[k] = in && out2 ? w2[c] : 0.f;
+        b2v[k] = in && out2 ? b2[c] : 0.f;
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) s += yv[k];
+    float mean = ln_block_sum(s, red) / (float)width;
+    float q = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) {
+        const float d = threadIdx.x + 256 * k < width ? yv[k] - mean : 0.f;
+        q += d * d;
+    }
+    float rstd = 1.0f / sqrtf(ln_block_sum(q, red) / (float)width + eps);
+    s = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) {
+        const int c = threadIdx.x + 256 * k;
+        if (c < width) {
+            xv[k] += mult * ((yv[k] - mean) * rstd * wv[k] + bv[k]);
+            x[base + c] = xv[k];
+            s += xv[k];
+        }
+    }
+    if (!out2) return;
+    mean = ln_block_sum(s, red) / (float)width;
+    q = 0.f;
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) {
+        const float d = threadIdx.x + 256 * k < width ? xv[k] - mean : 0.f;
+        q += d * d;
+    }
+    rstd = 1.0f / sqrtf(ln_block_sum(q, red) / (float)width + eps);
+#pragma unroll
+    for (int k = 0; k < kLnPerThread; ++k) {
+        const int c = threadIdx.x + 256 * k;
+        if (c < width) out2[base + c] = DT<T>::from_f((xv[k] - mean) * rstd * w2v[k] + b2v[k]);
+    }
+}
+
 template <typename T>
 __global__ void concat_cast_kernel(const float* __restrict__ a, const float* __restrict__ b, T* __restrict__ out, int width) {
     const size_t t = blockIdx.x;
@@ -140,6 +199,14 @@ extern "C" int b200_layernorm_residual(float* x, const float* y, int n_rows, int
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return B200_EUNSUPPORTED;
     cudaStream_t s = (cudaStream_t)stream;
+    if (width <= 256 * kLnPerThread && (out_dtype == B200_BF16 || out_dtype == B200_F32)) {
+        if (out_dtype == B200_BF16)
+            layernorm_residual_reg_kernel<__nv_bfloat16><<<n_rows, 256, 0, s>>>(x, y, width, eps, mult, w, b, w2, b2, (__nv_bfloat16*)out2);
+        else
+            layernorm_residual_reg_kernel<float><<<n_rows, 256, 0, s>>>(x, y, width, eps, mult, w, b, w2, b2, (float*)out2);
+        count_launch();
+        return (int)cudaGetLastError();
+    }
     if (out_dtype == B200_BF16) {
         static unsigned long long done = 0;
         if (smem > 48 * 1024) ensure_max_dynamic_smem((const void*)layernorm_residual_kernel<__nv_bfloat16>, 200 * 1024, done);

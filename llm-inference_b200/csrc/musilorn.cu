@@ -25,7 +25,9 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
+#include <map>
 
 #include "checkpoint_upload.h"
 #include "common.cuh"
@@ -70,6 +72,7 @@ class Musilorn : public Model {
 public:
     ~Musilorn() override {
         if (stream_) cudaStreamSynchronize(stream_);
+        drop_graphs();
         for (void* p : owned_) cudaFree(p);
         cudaFree(scratch_);
         cudaFree(ws_);
@@ -123,6 +126,11 @@ private:
     int parse_rot(const Json& mx, int dim, int layout, MuRot& rot, std::string& err);
     int gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi = B200_GG_NONE);
     int ensure_scratch(int T, int W);
+    int enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err);
+    void drop_graphs() {
+        for (auto& kv : graphs_) cudaGraphExecDestroy(kv.second.exec);
+        graphs_.clear();
+    }
 
     int dtype_ = B200_BF16, vocab_ = 0, D_ = 0;
     float eps_ = 1e-5f, mult_ = 1.f, logit_cap_ = 0.f;
@@ -150,6 +158,13 @@ private:
     size_t logits_host_floats_ = 0;
     int max_in_ = 0, max_q_ = 0, max_att_ = 0, max_ff_ = 0, freq_floats_ = 0;   // maxima over layers (scratch sizes)
     std::vector<int> freq_off_;   // first float of each frequency set's cos table in cs_ (per token: see step)
+    // CUDA graphs of single-token steps, by batch shape
+    struct StepGraph { cudaGraphExec_t exec; int launches; };
+    std::map<uint64_t, StepGraph> graphs_;
+    std::map<uint64_t, int> graph_seen_;
+    uint64_t buffers_epoch_ = 0, graph_epoch_ = 0;   // bumped whenever a buffer the captured launches point into is reallocated
+    const int* graph_tables_ = nullptr;              // the per-step tables the graphs read
+    bool graphs_enabled_ = true, capturing_ = false;
     bool capture_on_ = false;
     float* capture_ = nullptr;
     size_t capture_cap_ = 0;
@@ -219,6 +234,10 @@ int Musilorn::load(const ModelDir& dir, const b200_model_options& opt, std::stri
     logit_cap_ = (float)c.number("logit_softcap", 0.0);
     if (opt.max_tokens < 1 || opt.max_slots < 1) { err = "max_tokens and max_slots must be positive"; return B200_EINVAL; }
     if (cudaStreamCreateWithFlags(&stream_, cudaStreamNonBlocking) != cudaSuccess) { err = "no CUDA device: this library has no CPU path"; return B200_EINVAL; }
+    {
+        const char* e = getenv("B200_NO_GRAPH");   // 1: every step as plain launches
+        graphs_enabled_ = !(e && e[0] == '1');
+    }
     SafeTensorsFile st;
     if (!st.open(dir.path + "/model.safetensors", err)) return B200_EINVAL;
     // the design has no position limit of its own: a sequence can grow as long as the pool has pages
@@ -383,6 +402,7 @@ int Musilorn::ensure_scratch(int T, int W) {
     if (T <= cap_T_ && W <= cap_W_) return B200_OK;
     const int cT = std::max(T, cap_T_), cW = std::max(W, cap_W_);
     cudaStreamSynchronize(stream_);
+    ++buffers_epoch_;
     cudaFree(scratch_);
     scratch_ = nullptr;
     cap_T_ = cap_W_ = 0;
@@ -429,8 +449,9 @@ int Musilorn::ensure_scratch(int T, int W) {
 // y[M, N] = A[M, K] W[N, K]^T, contiguous; A and W of the serving dtype: the tcgen05 GEMM when it fits, else the grouped one
 int Musilorn::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N, int K, int epi) {
     const size_t need = b200_linear_ex_workspace_bytes(M, N, K);
-    if (need > ws_bytes_) {
+    if (need > ws_bytes_ && !capturing_) {
         cudaStreamSynchronize(stream_);
+        ++buffers_epoch_;
         cudaFree(ws_);
         ws_ = nullptr;
         ws_bytes_ = 0;
@@ -439,43 +460,11 @@ int Musilorn::gemm(const void* A, const void* W, void* C, int c_dt, int M, int N
     return b200_linear_ex(A, W, C, M, N, K, dtype_, c_dt, epi, ws_, ws_bytes_, stream_);
 }
 
-int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) {
-    if (entries.empty()) return B200_OK;
-    const uint64_t launches0 = b200_launch_count();
-    MU_TRY(seq_.begin_step(entries, stream_, err));
-    const int T = seq_.n_tokens, W = seq_.n_want, D = D_, dt = dtype_;
-    if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
-    int longest_entry = 0, longest_context = 0;
-    for (const StepEntry& en : entries) {
-        longest_entry = std::max(longest_entry, en.n_tokens);
-        longest_context = std::max(longest_context, seq_.length[en.slot]);
-    }
-    {   // room for the shares of split contexts (batches of few rows) and for the chunk states of long retention entries
-        size_t need = 0;
-        for (const MuLayer& L : layers_)
-            need = std::max(need, L.attention ? b200_paged_attention_workspace_bytes(T, L.heads, L.vdim)
-                                              : b200_retention_workspace_bytes(T, seq_.n_entries, L.heads, L.dim, L.vdim));
-        if (need > attn_ws_bytes_) {
-            cudaStreamSynchronize(stream_);
-            cudaFree(attn_ws_);
-            attn_ws_ = nullptr;
-            attn_ws_bytes_ = 0;
-            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
-        }
-    }
+// every launch of a step, in order, on stream_ (no synchronisation, no allocation: capturable into a graph)
+int Musilorn::enqueue(int T, int W, int longest_entry, int longest_context, bool want_ids, std::string& err) {
+    const int D = D_, dt = dtype_;
     const int* pages = seq_.pool.device();
     const int max_pages = seq_.pool.max_pages();
-    if (capture_on_) {
-        const size_t need = (size_t)runs_.size() * T * D;
-        if (capture_cap_ < need) {
-            cudaStreamSynchronize(stream_);
-            cudaFree(capture_);
-            capture_ = nullptr;
-            if (cudaMalloc(&capture_, need * 4) != cudaSuccess) { err = "step: no memory to keep the layers"; return B200_ENOMEM; }
-            capture_cap_ = need;
-        }
-        captured_tokens_ = T;
-    }
 #define MU_OP(call)                                                             \
     do {                                                                        \
         const int rc_ = (call);                                                 \
@@ -512,8 +501,9 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
             qa.pages = pages; qa.max_pages = max_pages; qa.page_rows = kPageRows;
             qa.slot = seq_.d_slot(); qa.pos = seq_.d_pos(); qa.start = seq_.d_start();
             qa.n_tokens = T; qa.heads = H; qa.kv_heads = L.kv_heads; qa.dim = L.dim; qa.dtype = dt;
+            qa.update_state_inline = longest_entry == 1;
             MU_OP(b200_qk_prepare(&qa, stream_));
-            if (L.conv_w && L.taps > 1)
+            if (L.conv_w && L.taps > 1 && longest_entry != 1)
                 MU_OP(b200_conv_state_update(proj_, L.n_in, R.state.data(), seq_.d_slot(), seq_.d_pos(), seq_.d_end(), T, L.n_in, L.taps, stream_));
             b200_paged_attention_args pa{};
             pa.q = q_; pa.out = att_; pa.k_pool = R.k_pool; pa.v_pool = R.v_pool;
@@ -563,7 +553,93 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
         MU_OP(b200_layernorm_pair(x_, seq_.d_want_rows(), W, D, eps_, fnw_, fnb_, hf_, nullptr, nullptr, nullptr, dt, stream_));
         MU_OP(gemm(hf_, head_, logits_, B200_F32, W, vocab_, D));
         if (logit_cap_ > 0.f) MU_OP(b200_softcap(logits_, (size_t)W * vocab_, logit_cap_, stream_));
-        if (ids_out) MU_OP(b200_argmax(logits_, ids_dev_, W, vocab_, B200_F32, stream_));
+        if (want_ids) MU_OP(b200_argmax(logits_, ids_dev_, W, vocab_, B200_F32, stream_));
+    }
+    return B200_OK;
+#undef MU_OP
+}
+
+int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int* ids_out, std::string& err) {
+    if (entries.empty()) return B200_OK;
+    const uint64_t launches0 = b200_launch_count();
+    MU_TRY(seq_.begin_step(entries, stream_, err));
+    const int T = seq_.n_tokens, W = seq_.n_want, D = D_;
+    if (ensure_scratch(T, std::max(W, 1)) != B200_OK) { err = "step: out of device memory for the scratch buffers"; return B200_ENOMEM; }
+    int longest_entry = 0, longest_context = 0;
+    for (const StepEntry& en : entries) {
+        longest_entry = std::max(longest_entry, en.n_tokens);
+        longest_context = std::max(longest_context, seq_.length[en.slot]);
+    }
+    {   // room for the shares of split contexts (batches of few rows) and for the chunk states of long retention entries
+        size_t need = 0;
+        for (const MuLayer& L : layers_)
+            need = std::max(need, L.attention ? b200_paged_attention_workspace_bytes(T, L.heads, L.vdim)
+                                              : b200_retention_workspace_bytes(T, seq_.n_entries, L.heads, L.dim, L.vdim));
+        if (need > attn_ws_bytes_) {
+            cudaStreamSynchronize(stream_);
+            ++buffers_epoch_;
+            cudaFree(attn_ws_);
+            attn_ws_ = nullptr;
+            attn_ws_bytes_ = 0;
+            if (cudaMalloc(&attn_ws_, need) == cudaSuccess) attn_ws_bytes_ = need;
+        }
+    }
+    if (capture_on_) {
+        const size_t need = (size_t)runs_.size() * T * D;
+        if (capture_cap_ < need) {
+            cudaStreamSynchronize(stream_);
+            cudaFree(capture_);
+            capture_ = nullptr;
+            if (cudaMalloc(&capture_, need * 4) != cudaSuccess) { err = "step: no memory to keep the layers"; return B200_ENOMEM; }
+            capture_cap_ = need;
+        }
+        captured_tokens_ = T;
+    }
+    // Batches of single tokens repeat their shape step after step: the second time a shape is seen its launch sequence is
+    // captured into a CUDA graph, from then on the step is one graph launch (the per-step tables are read through fixed
+    // pointers that begin_step refreshes). Anything that moves a buffer drops the graphs.
+    const bool want_ids = ids_out != nullptr;
+    if (buffers_epoch_ != graph_epoch_ || seq_.d_ids() != graph_tables_) {   // a buffer was reallocated (even to the same address:
+        drop_graphs();                                                         // the carving inside it changed)
+        graph_epoch_ = buffers_epoch_;
+        graph_tables_ = seq_.d_ids();
+    }
+    const bool graph_ok = graphs_enabled_ && longest_entry == 1 && !capture_on_ && T <= 4096 && W <= 4096;
+    const int ctx_bucket = longest_context > 256 ? std::min(16, (longest_context + 127) / 128) : 0;
+    const uint64_t key = (uint64_t)T | ((uint64_t)W << 16) | ((uint64_t)ctx_bucket << 32) | ((uint64_t)want_ids << 40);
+    int rc = B200_OK;
+    auto it = graph_ok ? graphs_.find(key) : graphs_.end();
+    if (it != graphs_.end()) {
+        if (cudaGraphLaunch(it->second.exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
+        count_launch(it->second.launches);
+    } else if (graph_ok && ++graph_seen_[key] >= 2) {
+        const uint64_t before = b200_launch_count();
+        capturing_ = true;
+        cudaGraph_t g = nullptr;
+        if (cudaStreamBeginCapture(stream_, cudaStreamCaptureModeThreadLocal) == cudaSuccess) {
+            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+            const cudaError_t ce = cudaStreamEndCapture(stream_, &g);
+            capturing_ = false;
+            cudaGraphExec_t exec = nullptr;
+            if (rc == B200_OK && ce == cudaSuccess && g && cudaGraphInstantiate(&exec, g, 0) == cudaSuccess) {
+                graphs_[key] = {exec, (int)(b200_launch_count() - before)};
+                if (cudaGraphLaunch(exec, stream_) != cudaSuccess) { err = "step: graph launch failed"; return B200_EINVAL; }
+            } else {   // not capturable here: run the launches directly, and do not try again
+                cudaGetLastError();
+                graphs_enabled_ = false;
+                rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+            }
+            if (g) cudaGraphDestroy(g);
+        } else {
+            capturing_ = false;
+            cudaGetLastError();
+            graphs_enabled_ = false;
+            rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+        }
+    } else
+        rc = enqueue(T, W, longest_entry, longest_context, want_ids, err);
+    if (rc != B200_OK) return rc;
+    if (W > 0) {
         if (logits_out) cudaMemcpyAsync(logits_host_, logits_, (size_t)W * vocab_ * 4, cudaMemcpyDeviceToHost, stream_);
         if (ids_out) cudaMemcpyAsync(ids_out, ids_dev_, (size_t)W * 4, cudaMemcpyDeviceToHost, stream_);
     }
@@ -572,7 +648,6 @@ int Musilorn::step(const std::vector<StepEntry>& entries, float* logits_out, int
     if (W > 0 && logits_out) memcpy(logits_out, logits_host_, (size_t)W * vocab_ * 4);
     launches_ = (int)(b200_launch_count() - launches0);
     return B200_OK;
-#undef MU_OP
 }
 
 Model* make_musilorn(const ModelDir& dir, const b200_model_options& opt, std::string& err) {

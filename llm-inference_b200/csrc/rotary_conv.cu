@@ -26,6 +26,7 @@ struct QkPrep {
     const float* q_norm; const float* k_norm; float eps;
     const float* cos; const float* sin; int rot_dims, rot_layout;
     void* q_out; void* k_pool; void* v_pool; int v_from_conv;
+    float* ring_out;   // non-NULL: every entry of the batch is one token, and the warp files its own inputs in the ring
     const int* pages; int max_pages, page_rows;
     const int* slot; const int* pos; const int* start;
     int heads, kv_heads, dim;
@@ -63,6 +64,8 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
                                                : a.conv_state[((size_t)b * (taps - 1) + src % (taps - 1)) * channels + c];
                 y = fmaf(a.conv_w[(size_t)c * taps + j], uin, y);
             }
+            // a one-token entry: nobody else reads this sequence's ring in this launch, and this lane has read its own places
+            if (a.ring_out && taps > 1) a.ring_out[((size_t)b * (taps - 1) + p % (taps - 1)) * channels + c] = a.proj[(size_t)t * a.ld_proj + c];
         } else
             y = a.proj[(size_t)t * a.ld_proj + c];
         if (is_k && a.v_from_conv) reinterpret_cast<T*>(a.v_pool)[cache_row * dim + i] = DT<T>::from_f(y);
@@ -116,7 +119,7 @@ extern "C" int b200_qk_prepare(const b200_qk_prepare_args* p, void* stream) {
     if (p->rot_layout != B200_ROPE_HALF && p->rot_layout != B200_ROPE_INTERLEAVED) return B200_EINVAL;
     if (p->n_tokens == 0) return B200_OK;
     QkPrep a{p->proj, p->ld_proj, p->conv_w, p->taps, p->conv_state, p->q_norm, p->k_norm, p->eps, p->cos, p->sin, p->rot_dims,
-             p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
+             p->rot_layout, p->q_out, p->k_pool, p->v_pool, p->v_from_conv, p->update_state_inline ? const_cast<float*>(p->conv_state) : nullptr, p->pages, p->max_pages, p->page_rows, p->slot, p->pos,
              p->start, p->heads, p->kv_heads, p->dim};
     if (a.conv_w && a.taps == 1) a.conv_state = a.proj;   // never read: every input of a one-tap filter is the token's own
     const long long units = (long long)p->n_tokens * (p->heads + p->kv_heads);

@@ -28,7 +28,7 @@ class QkPrepareArgs(C.Structure):
                 ("q_norm", _vp), ("k_norm", _vp), ("eps", _f), ("cos", _vp), ("sin", _vp), ("rot_dims", _i), ("rot_layout", _i),
                 ("q_out", _vp), ("k_pool", _vp), ("v_pool", _vp), ("v_from_conv", _i),
                 ("pages", _vp), ("max_pages", _i), ("page_rows", _i), ("slot", _vp), ("pos", _vp), ("start", _vp),
-                ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i)]
+                ("n_tokens", _i), ("heads", _i), ("kv_heads", _i), ("dim", _i), ("dtype", _i), ("update_state_inline", _i)]
 
 
 class PagedAttentionArgs(C.Structure):

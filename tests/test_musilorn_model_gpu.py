@@ -309,6 +309,32 @@ def test_a_long_prompt_in_one_step_and_in_large_portions(S, models, kind):
     m.close()
 
 
+@pytest.mark.parametrize("kind", ["f32", "bf16"])
+def test_repeated_single_token_steps_while_buffers_grow(S, models, kind):
+    """single-token steps of one shape repeat (the engine replays them as a captured graph); in between a longer
+    portion arrives and makes the scratch buffers grow, contexts pass 256 and 384 tokens (other splits of the decoding
+    attention), and two sequences decode side by side"""
+    folder, oracle, cfg = models["wide"]
+    m = open_model(S, folder, kind, max_tokens=2048)
+    V = cfg["vocab"]
+    a, b = tokens(420, V, 60), tokens(770, V, 61)
+    wa, wb = oracle.forward(a).numpy(), oracle.forward(b).numpy()
+    got_a = [m.step([(0, a[:5], [4])])]
+    for p in range(5, 12):                                   # one shape, seven times
+        got_a.append(m.step([(0, [a[p]], [0])]))
+    got_b = [m.step([(1, b[:600], [599])])]                  # the buffers grow
+    for p in range(12, 20):
+        got_a.append(m.step([(0, [a[p]], [0])]))
+    got_a.append(m.step([(0, a[20:250], [229])]))
+    for p in range(250, 420):                                # across 256 and 384 tokens of context, beside the other sequence
+        out = m.step([(0, [a[p]], [0]), (1, [b[350 + p]], [0])])
+        got_a.append(out[:1])
+        got_b.append(out[1:])
+    check(np.concatenate(got_a), wa[[4] + list(range(5, 20)) + [249] + list(range(250, 420))], kind)
+    check(np.concatenate(got_b), wb[[599] + list(range(600, 770))][: len(got_b)], kind)
+    m.close()
+
+
 def test_bad_steps_are_refused(S, models):
     folder, _, cfg = models["mix"]
     m = open_model(S, folder, "f32", max_tokens=128, slots=2)

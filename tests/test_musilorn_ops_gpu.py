@@ -63,7 +63,7 @@ def gen(seed):
     return torch.Generator().manual_seed(seed)
 
 
-@pytest.mark.parametrize("width", [1, 48, 1000])
+@pytest.mark.parametrize("width", [1, 48, 1000, 2048, 2049, 5000])
 @pytest.mark.parametrize("kind", ["f32", "bf16"])
 def test_layernorm_residual_and_next_norm(S, width, kind):
     code, g = code_of(S, kind), gen(width)
@@ -143,7 +143,8 @@ def test_qk_prepare_over_portions_with_carried_inputs(S, kind, heads, kv, dim, t
     state = torch.full((2, max(taps - 1, 1), ch), 1e4)        # stale inputs of an earlier owner
     kp, vp = (torch.full((n_pages * PR, kv, dim), 7.0, dtype=tdt(S, code), device="cuda") for _ in range(2))
     state_d, pages_d, cw_d, qn_d, kn_d = dev(state), dev(pages), dev(cw), dev(qn), dev(kn)
-    plan = [[(0, 3), (1, 1)], [(0, 1), (1, 2)], [(1, 4)], [(0, 7)]]
+    # steps in which every sequence brings one token file their inputs in the ring inside the same launch
+    plan = [[(0, 3), (1, 1)], [(0, 1), (1, 1)], [(0, 1), (1, 1)], [(1, 4)], [(0, 6)]]
     at = {0: 0, 1: 0}
     got_q = {0: [], 1: []}
     for step in plan:
@@ -162,9 +163,11 @@ def test_qk_prepare_over_portions_with_carried_inputs(S, kind, heads, kv, dim, t
         a = S.QkPrepareArgs(proj.data_ptr(), ch, cw_d.data_ptr(), taps, state_d.data_ptr(), qn_d.data_ptr(), kn_d.data_ptr(), 1e-5,
                             cs.data_ptr(), sn.data_ptr(), rot_dims, S.ROPE_HALF if layout == "half" else S.ROPE_INTERLEAVED,
                             q_out.data_ptr(), kp.data_ptr(), vp.data_ptr(), 1, pages_d.data_ptr(), max_pages, PR,
-                            ints(slot).data_ptr(), ints(pos).data_ptr(), ints(start).data_ptr(), T, heads, kv, dim, code)
+                            ints(slot).data_ptr(), ints(pos).data_ptr(), ints(start).data_ptr(), T, heads, kv, dim, code,
+                            int(all(n == 1 for _, n in step)))
         sync_ok(S.lib().b200_qk_prepare(C.byref(a), None))
-        sync_ok(S.lib().b200_conv_state_update(proj.data_ptr(), ch, state_d.data_ptr(), ints(slot).data_ptr(), ints(pos).data_ptr(),
+        if not all(n == 1 for _, n in step):
+            sync_ok(S.lib().b200_conv_state_update(proj.data_ptr(), ch, state_d.data_ptr(), ints(slot).data_ptr(), ints(pos).data_ptr(),
                                                ints(end).data_ptr(), T, ch, taps, None))
         r = 0
         for b, n in step:
