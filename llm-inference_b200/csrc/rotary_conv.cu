@@ -35,7 +35,7 @@ struct QkPrep {
 // One warp per (token, head unit): units [0, heads) are query heads, [heads, heads + kv_heads) key heads; a lane owns the
 // dimensions lane, lane + 32, ... (coalesced loads and stores); the head's sum of squares is a warp reduction and the
 // rotation reads its partner through the warp's slice of shared memory, so no CTA-wide barrier is needed.
-constexpr int kPrepWarps = 4;
+constexpr int kPrepWarps = 4, kMaxTapsUnrolled = 4;   // longer filters take the plain loop
 template <typename T>
 __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPrep a, int n_units) {
     extern __shared__ float prep_sm[];
@@ -52,6 +52,37 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
     if (is_k) cache_row = ((size_t)a.pages[(size_t)b * a.max_pages + p / a.page_rows] * a.page_rows + p % a.page_rows) * a.kv_heads + (u - a.heads);
     const int first = a.conv_w ? a.start[t] : 0, taps = a.taps;
     float ss = 0.f;
+    if (a.conv_w && taps <= kMaxTapsUnrolled) {
+        // four dimensions per lane and all their taps at once: every load of the group is in flight before the first sum
+        for (int i0 = lane; i0 < dim; i0 += 128) {
+            float xin[4][kMaxTapsUnrolled], w[4][kMaxTapsUnrolled];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + 32 * k, c = ch0 + i;
+#pragma unroll
+                for (int j = 0; j < kMaxTapsUnrolled; ++j) {
+                    const int back = taps - 1 - j, src = p - back;
+                    const bool live = i < dim && j < taps && src >= 0;
+                    xin[k][j] = !live ? 0.f
+                              : src >= first ? a.proj[(size_t)(t - back) * a.ld_proj + c]
+                                             : a.conv_state[((size_t)b * (taps - 1) + src % (taps - 1)) * channels + c];
+                    w[k][j] = live ? a.conv_w[(size_t)c * taps + j] : 0.f;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = i0 + 32 * k, c = ch0 + i;
+                if (i >= dim) continue;
+                float y = 0.f;
+#pragma unroll
+                for (int j = 0; j < kMaxTapsUnrolled; ++j) y = fmaf(w[k][j], xin[k][j], y);
+                if (a.ring_out && taps > 1) a.ring_out[((size_t)b * (taps - 1) + p % (taps - 1)) * channels + c] = a.proj[(size_t)t * a.ld_proj + c];
+                if (is_k && a.v_from_conv) reinterpret_cast<T*>(a.v_pool)[cache_row * dim + i] = DT<T>::from_f(y);
+                vals[i] = y;
+                ss += y * y;
+            }
+        }
+    } else
     for (int i = lane; i < dim; i += 32) {
         const int c = ch0 + i;
         float y;

@@ -289,7 +289,7 @@ def random_musilorn(width, heads, kv_heads, dim, ff, n_layers, vocab, retention_
     def rnd(*shape, s=None):
         return (torch.randn(*shape, generator=g) * (s if s is not None else 1.0 / math.sqrt(shape[-1]))).to(torch.bfloat16)
 
-    cfg = dict(architecture="Musilorn", vocab=vocab, width=width, norm=dict(eps=1e-6), residual_mult=0.5, logit_softcap=30.0, layers=[])
+    cfg = dict(architecture="Musilorn", vocab=vocab, width=width, norm=dict(eps=1e-5), residual_mult=0.5, logit_softcap=25.0, layers=[])
     w = {"embed": rnd(vocab, width, s=1.0), "head": rnd(vocab, width), "final.norm": torch.ones(width), "final.norm.b": torch.zeros(width)}
     if loop:
         cfg["loop"] = dict(start=loop[0], stop=loop[1], times=loop[2])

@@ -12,7 +12,7 @@ import musilorn_oracle as O
 
 pytestmark = pytest.mark.gpu
 
-SCALING = dict(factor=4.0, low=1.0, high=4.0, original=64)
+SCALING = dict(factor=8.0, low=1.0, high=3.0, original=64)
 SHAPES = {
     # the span [attention, retention] runs twice, then one more attention layer; grouped heads, scaled frequencies
     "mix": dict(width=48, vocab=61, loop=(0, 2, 2), layers=[
@@ -34,7 +34,7 @@ SHAPES = {
     # heads as wide as the tensor-core tiles take them, a value size above one warp pass, a span of one layer
     "wide": dict(width=64, vocab=50, loop=(0, 1, 2), layers=[
         dict(type="attention", heads=4, kv_heads=2, dim=64, conv=4, scaling=SCALING, ff=128),
-        dict(type="retention", heads=2, dim=32, vdim=72, decay=[0.96875, 0.999], ff=None),
+        dict(type="retention", heads=2, dim=32, vdim=72, decay=[0.95, 0.999], ff=None),
         dict(type="attention", heads=2, kv_heads=1, dim=128, conv=2, ff=None)]),
 }
 RTOL = {"f32": 2e-4, "bf16": 6e-2}

@@ -91,8 +91,8 @@ def test_concat_softcap_and_embedding_without_positions(S):
         assert torch.equal(out.cpu(), torch.cat([a, b], 1).to(tdt(S, code)))
     v = torch.randn(1000, generator=g) * 40
     vd = dev(v)
-    sync_ok(S.lib().b200_softcap(vd.data_ptr(), 1000, 15.0, None))
-    assert rel(vd, O.capped(v.double(), 15.0)) < 1e-6
+    sync_ok(S.lib().b200_softcap(vd.data_ptr(), 1000, 11.0, None))
+    assert rel(vd, O.capped(v.double(), 11.0)) < 1e-6
     table = torch.randn(9, 12, generator=g)
     out = torch.empty(4, 12, device="cuda")
     sync_ok(S.lib().b200_embed_positions(ints([8, 0, 3, 3]).data_ptr(), None, dev(table).data_ptr(), None, out.data_ptr(), 4, 12, S.F32, None))
@@ -293,7 +293,7 @@ def test_a_far_key_stands_out_and_the_sink_weighs_in(S, kind, far):
 
 
 @pytest.mark.parametrize("heads,dim,vdim,rot_dims,layout", [(3, 8, 12, 8, "half"), (1, 4, 4, 2, "interleaved"), (2, 40, 70, 0, "half"),
-                                                            (2, 32, 64, 32, "half")])
+                                                            (2, 32, 96, 32, "half")])
 def test_retention_in_portions_with_a_carried_state(S, heads, dim, vdim, rot_dims, layout):
     g = gen(dim + vdim)
     lens = {0: 300, 1: 45, 2: 3}
