@@ -53,31 +53,48 @@ __global__ void __launch_bounds__(kPrepWarps * 32) qk_prepare_kernel(const QkPre
     const int first = a.conv_w ? a.start[t] : 0, taps = a.taps;
     float ss = 0.f;
     if (a.conv_w && taps <= kMaxTapsUnrolled) {
-        // four dimensions per lane and all their taps at once: every load of the group is in flight before the first sum
+        // The rows that hold the taps' inputs (this step's batch, the slot's ring, or nothing before position 0) are found
+        // once per warp; then four dimensions per lane and all their taps at once: every load of the group is in flight
+        // before the first sum. A four-tap filter is one 16-byte load per channel.
+        const float* rows[kMaxTapsUnrolled];
+        bool ok[kMaxTapsUnrolled];
+#pragma unroll
+        for (int j = 0; j < kMaxTapsUnrolled; ++j) {
+            const int back = taps - 1 - j, src = p - back;
+            ok[j] = j < taps && src >= 0;
+            rows[j] = !ok[j] ? a.proj
+                      : src >= first ? a.proj + (size_t)(t - back) * a.ld_proj + ch0
+                                     : a.conv_state + ((size_t)b * (taps - 1) + src % (taps - 1)) * channels + ch0;
+        }
+        const float* cw = a.conv_w + (size_t)ch0 * taps;
+        const bool w4 = taps == 4 && (reinterpret_cast<uintptr_t>(a.conv_w) & 15u) == 0;
+        float* ring = (a.ring_out && taps > 1) ? a.ring_out + ((size_t)b * (taps - 1) + p % (taps - 1)) * channels + ch0 : nullptr;
+        T* vdst = (is_k && a.v_from_conv) ? reinterpret_cast<T*>(a.v_pool) + cache_row * dim : nullptr;
         for (int i0 = lane; i0 < dim; i0 += 128) {
             float xin[4][kMaxTapsUnrolled], w[4][kMaxTapsUnrolled];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int i = i0 + 32 * k, c = ch0 + i;
+                const int i = i0 + 32 * k;
+                const bool in = i < dim;
 #pragma unroll
-                for (int j = 0; j < kMaxTapsUnrolled; ++j) {
-                    const int back = taps - 1 - j, src = p - back;
-                    const bool live = i < dim && j < taps && src >= 0;
-                    xin[k][j] = !live ? 0.f
-                              : src >= first ? a.proj[(size_t)(t - back) * a.ld_proj + c]
-                                             : a.conv_state[((size_t)b * (taps - 1) + src % (taps - 1)) * channels + c];
-                    w[k][j] = live ? a.conv_w[(size_t)c * taps + j] : 0.f;
+                for (int j = 0; j < kMaxTapsUnrolled; ++j) xin[k][j] = in && ok[j] ? rows[j][i] : 0.f;
+                if (w4) {
+                    const float4 w4v = in ? *reinterpret_cast<const float4*>(cw + (size_t)i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    w[k][0] = w4v.x; w[k][1] = w4v.y; w[k][2] = w4v.z; w[k][3] = w4v.w;
+                } else {
+#pragma unroll
+                    for (int j = 0; j < kMaxTapsUnrolled; ++j) w[k][j] = in && j < taps ? cw[(size_t)i * taps + j] : 0.f;
                 }
             }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
-                const int i = i0 + 32 * k, c = ch0 + i;
+                const int i = i0 + 32 * k;
                 if (i >= dim) continue;
                 float y = 0.f;
 #pragma unroll
                 for (int j = 0; j < kMaxTapsUnrolled; ++j) y = fmaf(w[k][j], xin[k][j], y);
-                if (a.ring_out && taps > 1) a.ring_out[((size_t)b * (taps - 1) + p % (taps - 1)) * channels + c] = a.proj[(size_t)t * a.ld_proj + c];
-                if (is_k && a.v_from_conv) reinterpret_cast<T*>(a.v_pool)[cache_row * dim + i] = DT<T>::from_f(y);
+                if (ring) ring[i] = a.proj[(size_t)t * a.ld_proj + ch0 + i];   // the token's own input (the last tap)
+                if (vdst) vdst[i] = DT<T>::from_f(y);
                 vals[i] = y;
                 ss += y * y;
             }
