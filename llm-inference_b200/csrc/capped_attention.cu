@@ -353,8 +353,9 @@ __device__ __forceinline__ void pa_ldsm_x4_trans(uint32_t (&r)[4], const void* p
     const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
+// (not volatile: a pure function of its registers, so the compiler may interleave independent accumulators)
 __device__ __forceinline__ void pa_mma(float (&d)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
@@ -443,16 +444,23 @@ __global__ void __launch_bounds__(128, D <= 128 ? 3 : 1) paged_attn_tile_kernel(
             const bf* Vb = Vs + buf * kTileN * RS;
             float s[kTileN / 8][4];
 #pragma unroll
-            for (int nt = 0; nt < kTileN / 8; ++nt) {
-                s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-                // one ldmatrix.x4 brings the K fragments of two k steps: matrices (k 0-7 | 8-15 | 16-23 | 24-31) of 8 keys
-                const bf* kaddr = Kb + (nt * 8 + (lane & 7)) * RS + (lane >> 3) * 8;
+            for (int nt = 0; nt < kTileN / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+            // k steps outside, key columns inside: consecutive MMAs feed different accumulators. One ldmatrix.x4 brings the
+            // K fragments of two k steps: matrices (k 0-7 | 8-15 | 16-23 | 24-31) of 8 keys
 #pragma unroll
-                for (int ks = 0; ks < D / 16; ks += 2) {
-                    uint32_t b4[4];
-                    pa_ldsm_x4(b4, kaddr + ks * 16);
-                    const uint32_t b0[2] = {b4[0], b4[1]}, b1[2] = {b4[2], b4[3]};
+            for (int ks = 0; ks < D / 16; ks += 2) {
+                uint32_t b4[kTileN / 8][4];
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt)
+                    pa_ldsm_x4(b4[nt], Kb + (nt * 8 + (lane & 7)) * RS + (lane >> 3) * 8 + ks * 16);
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt) {
+                    const uint32_t b0[2] = {b4[nt][0], b4[nt][1]};
                     pa_mma(s[nt], qf[ks], b0);
+                }
+#pragma unroll
+                for (int nt = 0; nt < kTileN / 8; ++nt) {
+                    const uint32_t b1[2] = {b4[nt][2], b4[nt][3]};
                     pa_mma(s[nt], qf[ks + 1], b1);
                 }
             }
